@@ -39,11 +39,12 @@ from .pages import PagePool
 
 @dataclasses.dataclass
 class PagedCacheView:
-    pool: torch.Tensor          # [pages, entries, 2, kv_heads, page_size, head_dim]
+    pool: torch.Tensor          # [pages, entries, 2, kv_heads, page_size, head_dim], or flat (PagedKVSpec.value_dim)
     layer: int                  # index of this entry inside the group
     block_table: torch.Tensor   # int32 [max_seqs, max_pages_per_seq]
     page_size: int
     writable: bool = True
+    spec: Optional[PagedKVSpec] = None
 
 
 @dataclasses.dataclass
@@ -71,8 +72,11 @@ class PagedGroup:
         self.spec, self.entries, self.page_size = spec, entries, page_size
         self.max_pages_per_seq = max_pages_per_seq
         self.pool = PagePool(num_pages)
-        self.kv = torch.zeros((num_pages, len(entries), 2, spec.num_kv_heads, page_size, spec.head_dim),
-                              dtype=dtype, device=device)
+        if spec.value_dim is None:
+            shape = (num_pages, len(entries), 2, spec.num_kv_heads, page_size, spec.head_dim)
+        else:
+            shape = (num_pages, len(entries), spec.num_kv_heads * page_size * (spec.head_dim + spec.value_dim))
+        self.kv = torch.zeros(shape, dtype=dtype, device=device)
         self.block_table = torch.full((max_seqs, max_pages_per_seq), -1, dtype=torch.int32, device=device)
         # per slot: logical page index -> page id, and the first logical page still held
         self.pages: List[Dict[int, int]] = [dict() for _ in range(max_seqs)]
@@ -81,21 +85,31 @@ class PagedGroup:
 
     @property
     def bytes_per_token(self) -> int:
-        return len(self.entries) * 2 * self.spec.num_kv_heads * self.spec.head_dim * self.kv.element_size()
+        per_head = 2 * self.spec.head_dim if self.spec.value_dim is None else self.spec.head_dim + self.spec.value_dim
+        return len(self.entries) * self.spec.num_kv_heads * per_head * self.kv.element_size()
 
     def _first_needed_page(self, start: int) -> int:
         """Lowest logical page that queries at positions >= start can read."""
-        if self.spec.window is None:
-            return 0
-        return max(0, start - self.spec.window + 1) // self.page_size
+        first = 0
+        if self.spec.window is not None:
+            first = max(0, start - self.spec.window + 1)
+        if self.spec.block is not None:
+            first = max(first, start // self.spec.block * self.spec.block)
+        return first // self.page_size
+
+    @property
+    def _reach(self) -> Optional[int]:
+        """The most positions back a query can read, itself included (None: all)."""
+        limits = [n for n in (self.spec.window, self.spec.block) if n is not None]
+        return min(limits) if limits else None
 
     def peak_pages(self, end: int, portion: int) -> int:
         """The most pages a request holds at any time while it is brought to ``end`` tokens in portions of at
         most ``portion``: all of them, or what a window and one portion span."""
         total = (end + self.page_size - 1) // self.page_size
-        if self.spec.window is None:
+        if self._reach is None:
             return total
-        return min(total, (self.spec.window - 1 + portion + self.page_size - 1) // self.page_size + 1)
+        return min(total, (self._reach - 1 + portion + self.page_size - 1) // self.page_size + 1)
 
     def missing(self, slot: int, start: int, end: int) -> List[int]:
         """Logical pages that positions start..end-1 need and the slot does not hold."""
@@ -125,8 +139,9 @@ class PagedGroup:
             self.updates[slot * self.max_pages_per_seq + j] = -1
 
     def trim(self, slot: int, length: int) -> int:
-        """Give back the pages that no query at a position >= length can read (window groups)."""
-        if self.spec.window is None:
+        """Give back the pages that no query at a position >= length can read (groups with a window or a
+        block-diagonal mask)."""
+        if self._reach is None:
             return 0
         first = self._first_needed_page(length)
         gone = [j for j in self.pages[slot] if j < first]
@@ -151,26 +166,44 @@ class CacheManager:
         self.dtype, self.page_size, self.max_seqs, self.max_seq_len = dtype, page_size, max_seqs, max_seq_len
         self.max_pages_per_seq = (max_seq_len + page_size - 1) // page_size
         self.groups: List[PagedGroup] = []
-        self.states: Dict[int, torch.Tensor] = {}
+        self.states: Dict[Any, torch.Tensor] = {}       # entry index (or (entry, component)) -> [max_seqs, *shape]
         self._entries: List[Optional[_Entry]] = [None] * len(cache_specs)
-        by_spec: Dict[PagedKVSpec, List[int]] = {}
-        for i, spec in enumerate(cache_specs):
-            if isinstance(spec, PagedKVSpec):
-                by_spec.setdefault(spec, []).append(i)
+        # A cache entry needs one thing (pages, a state, nothing) or several (a tuple, possibly of tuples: a mixer
+        # with keys in pages and a state beside them, wrapped by a part with a state of its own); every single
+        # need is a leaf, known by its path (entry, component, ...), and the layer step gets views nested alike.
+        makers: Dict[Any, Any] = {}
+        by_spec: Dict[PagedKVSpec, List[Any]] = {}
+
+        def walk(key, spec):
+            if isinstance(spec, (tuple, list)):
+                for j, sub in enumerate(spec):
+                    walk(key + (j,), sub)
+            elif isinstance(spec, PagedKVSpec):
+                by_spec.setdefault(spec, []).append(key)
             elif isinstance(spec, StateSpec):
                 t = torch.zeros((max_seqs,) + tuple(spec.shape), dtype=spec.dtype, device=self.device)
-                self.states[i] = t
-                self._entries[i] = _Entry(lambda w, t=t: StateView(t, w))
+                self.states[key[0] if len(key) == 1 else key] = t
+                makers[key] = lambda w, t=t: StateView(t, w)
             elif spec is None:
-                self._entries[i] = _Entry(lambda w: None)
+                makers[key] = lambda w: None
             else:
-                raise TypeError(f"cache entry {i}: unknown cache spec {spec!r}")
-        for spec, entries in by_spec.items():
-            g = PagedGroup(spec, entries, page_size, num_pages, max_seqs, self.max_pages_per_seq, dtype, self.device)
+                raise TypeError(f"cache entry {key[0]}: unknown cache spec {spec!r}")
+
+        def maker(key, spec):
+            if isinstance(spec, (tuple, list)):
+                subs = [maker(key + (j,), sub) for j, sub in enumerate(spec)]
+                return lambda w, subs=subs: tuple(m(w) for m in subs)
+            return makers[key]
+
+        for i, spec in enumerate(cache_specs):
+            walk((i,), spec)
+        for spec, keys in by_spec.items():
+            g = PagedGroup(spec, [k[0] if len(k) == 1 else k for k in keys], page_size, num_pages, max_seqs, self.max_pages_per_seq, dtype, self.device)
             self.groups.append(g)
-            for k, i in enumerate(entries):
-                self._entries[i] = _Entry(
-                    lambda w, g=g, k=k: PagedCacheView(g.kv, k, g.block_table, page_size, w))
+            for k, key in enumerate(keys):
+                makers[key] = lambda w, g=g, k=k: PagedCacheView(g.kv, k, g.block_table, page_size, w, g.spec)
+        for i, spec in enumerate(cache_specs):
+            self._entries[i] = _Entry(maker((i,), spec))
         self._free_slots = list(range(max_seqs - 1, -1, -1))
         self._live = [False] * max_seqs
         self.lengths = [0] * max_seqs

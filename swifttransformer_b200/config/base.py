@@ -115,8 +115,10 @@ def config_class(architecture: str) -> Type[ModelConfig]:
 
 def config_from_dict(raw: Dict[str, Any]) -> ModelConfig:
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]           # some designs name themselves with one string
     if not archs or not isinstance(archs, list):
-        raise ConfigError("config.json lacks 'architectures' (a list with the model class name)")
+        raise ConfigError("config.json lacks 'architectures' (a list with the model class name) or 'architecture'")
     return config_class(archs[0]).from_dict(raw)
 
 

@@ -97,6 +97,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == 1) return v > 0.f ? v : 0.f;                                // relu
     if (act == 2) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));  // gelu (erf form)
+    if (act == 3) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));  // gelu (tanh form)
+    if (act == 4) return v / (1.f + expf(-v));                              // silu
     return v;
 }
 

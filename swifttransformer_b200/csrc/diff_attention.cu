@@ -1,0 +1,278 @@
+// Differential attention over a paged cache: every query head carries two
+// score maps (two queries, two keys per key/value head) over one set of values.
+//
+//   s_a  = cap * tanh(scale * (q_a . k_a) / cap)          a = 1, 2   (cap <= 0: no cap)
+//   p_a  = softmax of s_a over the visible keys
+//   o    = p_1 V - lambda * p_2 V
+//   out  = o / sqrt(mean(o^2) + eps) * out_scale           (over the head's value dimensions)
+//
+// Visible keys of the query at position p: lo..p with lo = floor(p / block) * block when the mask is
+// block-diagonal (block > 0; blocks are counted from position 0 of the request), max(0, p - window + 1)
+// with a window, else 0.
+//
+// Cache layout (one page of one cache entry; kd = 2 * dim, the two maps' keys side by side):
+//   keys   [kv_head][position in page][kd]     at offset 0
+//   values [kv_head][position in page][vd]     at offset nkv * page_size * kd
+// kd and vd need not be equal.  Pages of an entry are `page_stride` elements apart.
+//
+// This file holds the preparation of q, k and v (short convolution over time, per-map RMS norm with a
+// shared weight, rotation of pairs of dimensions by position, cache write) and the plain attention kernel
+// (float arithmetic for either storage type, key tiles aligned to absolute positions: a row's result does not
+// depend on how the request was cut into steps or on what else is in the batch).
+#include "common.cuh"
+
+#define CONV_MAX_TAPS 8
+#define PREP_THREADS 256
+
+struct DiffCache {
+    int max_pages, page_size, nkv, kd, vd;
+    long long page_stride;      // elements between consecutive pages of this entry
+    long long entry_offset;     // elements from the pool's start to this entry's part of page 0
+};
+
+template <typename T>
+__device__ __forceinline__ T* cache_keys(T* pool, const DiffCache& c, int page, int kvh, int pip) {
+    return pool + c.entry_offset + (long long)page * c.page_stride + ((long long)kvh * c.page_size + pip) * c.kd;
+}
+template <typename T>
+__device__ __forceinline__ T* cache_values(T* pool, const DiffCache& c, int page, int kvh, int pip) {
+    return pool + c.entry_offset + (long long)page * c.page_stride + (long long)c.nkv * c.page_size * c.kd +
+           ((long long)kvh * c.page_size + pip) * c.vd;
+}
+
+// One warp per unit of a token: a unit is one map of one query head (dim channels), one map of one key head
+// (dim channels) or one value head (vd channels).  A lane owns pairs of neighbouring channels, so that a
+// rotated pair stays in one thread.
+//
+// proj:  [n_tokens, ld] the fused projection q | k | v as the product left it (before the convolution)
+// conv_w: [channels, taps] float, channels = nh*2*dim + nkv*2*dim + nkv*vd in the projection's order
+// state: [slots, taps-1, channels] float, read only (conv_state_update moves it afterwards)
+template <typename T>
+__global__ void __launch_bounds__(PREP_THREADS)
+diff_qkv_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
+                        const float* __restrict__ state, int taps, const float* __restrict__ q_norm,
+                        const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int rot_dims,
+                        T* __restrict__ q_out, T* __restrict__ pool, DiffCache cache,
+                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                        const int* __restrict__ q_start, const int* __restrict__ slots,
+                        const int* __restrict__ block_table, int nh, int dim, int write_kv, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos < 0) return;
+    const int b = seq_of_token[t];
+    const int slot = slots[b];
+    const int i = t - q_start[b];                         // the token's place in its portion
+    const int nkv = cache.nkv, vd = cache.vd;
+    const int q_units = nh * 2, k_units = nkv * 2, units = q_units + k_units + nkv;
+    const int channels = (q_units + k_units) * dim + nkv * vd;
+    const int keep = taps - 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int page = block_table[(size_t)slot * cache.max_pages + pos / cache.page_size];
+    const int pip = pos % cache.page_size;
+    if (page < 0 && write_kv && status && threadIdx.x == 0) *status = 1;
+    const float* st = state + (size_t)slot * keep * channels;
+    for (int u = warp; u < units; u += nwarp) {
+        const bool is_q = u < q_units, is_k = !is_q && u < q_units + k_units;
+        const int width = (is_q || is_k) ? dim : vd;
+        const int ch0 = is_q ? u * dim : is_k ? q_units * dim + (u - q_units) * dim
+                                              : (q_units + k_units) * dim + (u - q_units - k_units) * vd;
+        // at most 4 pairs per lane: widths up to 256
+        float x0[4], x1[4];
+        float ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            x0[r] = x1[r] = 0.f;
+            const int e = 2 * (lane + 32 * r);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                if (e + half >= width) continue;
+                const int c = ch0 + e + half;
+                float y = 0.f;
+                for (int j = 0; j < taps; ++j) {
+                    const int back = keep - j;            // the input `back` positions before this token
+                    float v;
+                    if (back <= i) v = to_f32(proj[(size_t)(t - back) * ld + c]);
+                    else v = st[(size_t)(keep - (back - i)) * channels + c];   // zero before the request's start
+                    y = fmaf(conv_w[(size_t)c * taps + j], v, y);
+                }
+                if (half) x1[r] = y; else x0[r] = y;
+                ss += y * y;
+            }
+        }
+        if (is_q || is_k) {
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)dim + eps);
+            const float* g = is_q ? q_norm : k_norm;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int e = 2 * (lane + 32 * r);
+                if (e >= dim) continue;
+                float a = x0[r] * inv * g[e];
+                float bb = e + 1 < dim ? x1[r] * inv * g[e + 1] : 0.f;
+                if (e + 1 < rot_dims) {
+                    float sn, cs;
+                    sincosf((float)pos * inv_freq[e >> 1], &sn, &cs);
+                    const float ra = a * cs - bb * sn, rb = bb * cs + a * sn;
+                    a = ra; bb = rb;
+                }
+                x0[r] = a; x1[r] = bb;
+            }
+        }
+        T* dst;
+        if (is_q) dst = q_out + ((size_t)t * q_units + u) * dim;
+        else if (!write_kv || page < 0) continue;
+        else if (is_k) dst = cache_keys(pool, cache, page, (u - q_units) >> 1, pip) + ((u - q_units) & 1) * dim;
+        else dst = cache_values(pool, cache, page, u - q_units - k_units, pip);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int e = 2 * (lane + 32 * r);
+            if (e < width) dst[e] = from_f32<T>(x0[r]);
+            if (e + 1 < width) dst[e + 1] = from_f32<T>(x1[r]);
+        }
+    }
+}
+
+ST_EXPORT int st_diff_qkv_prepare(const void* proj, int ld, const float* conv_w, const float* state, int taps,
+                                  const float* q_norm, const float* k_norm, float eps, const float* inv_freq,
+                                  int rot_dims, void* q_out, void* pool, long long page_stride, long long entry_offset,
+                                  const int* positions, const int* seq_of_token, const int* q_start, const int* slots,
+                                  const int* block_table, int max_pages, int n_tokens, int nh, int nkv, int dim, int vd,
+                                  int page_size, int write_kv, int* status, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || dim <= 0 || vd <= 0 || page_size <= 0 || taps < 1 || rot_dims < 0 ||
+        rot_dims > dim || rot_dims % 2)
+        return ST_ERR_BAD_ARG;
+    if (taps > CONV_MAX_TAPS || dim > 256 || vd > 256) return ST_ERR_TOO_LARGE;
+    const DiffCache c = {max_pages, page_size, nkv, 2 * dim, vd, page_stride, entry_offset};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == 0)
+        diff_qkv_prepare_kernel<float><<<n_tokens, PREP_THREADS, 0, s>>>((const float*)proj, ld, conv_w, state, taps, q_norm,
+            k_norm, eps, inv_freq, rot_dims, (float*)q_out, (float*)pool, c, positions, seq_of_token, q_start, slots,
+            block_table, nh, dim, write_kv, status);
+    else if (dtype == 1)
+        diff_qkv_prepare_kernel<bf16><<<n_tokens, PREP_THREADS, 0, s>>>((const bf16*)proj, ld, conv_w, state, taps, q_norm,
+            k_norm, eps, inv_freq, rot_dims, (bf16*)q_out, (bf16*)pool, c, positions, seq_of_token, q_start, slots,
+            block_table, nh, dim, write_kv, status);
+    else return ST_ERR_BAD_DTYPE;
+    return st_launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Plain differential attention: one block per (query token, head).
+#define KT 128   // keys per tile == threads per block
+
+__device__ __forceinline__ int first_visible(int pos, int block, int window) {
+    if (block > 0) return (pos / block) * block;
+    if (window > 0) return max(0, pos - window + 1);
+    return 0;
+}
+
+__device__ __forceinline__ float soft_cap(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
+template <typename T>
+__global__ void __launch_bounds__(KT)
+diff_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, DiffCache cache, T* __restrict__ out,
+                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                            const int* __restrict__ slots, const int* __restrict__ block_table, int nh, int dim,
+                            float scale, float cap, int block, int window, float lambda, float eps, float out_scale,
+                            int* __restrict__ status) {
+    extern __shared__ float smem[];
+    float* sq = smem;                 // [2 * dim] the two queries
+    float* sp1 = smem + 2 * dim;      // [KT] weights of the tile, map 1
+    float* sp2 = sp1 + KT;            // [KT] map 2
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int pos = positions[t];
+    if (pos < 0) return;
+    const int nkv = cache.nkv, vd = cache.vd, kd = cache.kd, ps = cache.page_size;
+    const int kvh = h / (nh / nkv);
+    const int* bt = block_table + (size_t)slots[seq_of_token[t]] * cache.max_pages;
+    for (int e = threadIdx.x; e < kd; e += KT) sq[e] = to_f32(q[((size_t)t * nh + h) * kd + e]);
+    __syncthreads();
+    const int lo = first_visible(pos, block, window), hi = pos + 1;
+    float a1[2] = {0.f, 0.f}, a2[2] = {0.f, 0.f};     // vd <= 2 * KT
+    float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.f, l2 = 0.f;
+    for (int base = (lo / KT) * KT; base < hi; base += KT) {
+        const int j = base + threadIdx.x;
+        const bool seen = j >= lo && j < hi;
+        float s1 = -INFINITY, s2 = -INFINITY;
+        if (seen) {
+            const int page = bt[j / ps];
+            if (page >= 0) {
+                const T* krow = cache_keys(pool, cache, page, kvh, j % ps);
+                float d1 = 0.f, d2 = 0.f;
+                for (int e = 0; e < dim; ++e) {
+                    d1 = fmaf(sq[e], to_f32(krow[e]), d1);
+                    d2 = fmaf(sq[dim + e], to_f32(krow[dim + e]), d2);
+                }
+                s1 = soft_cap(d1 * scale, cap);
+                s2 = soft_cap(d2 * scale, cap);
+            } else if (status) {
+                *status = 1;
+            }
+        }
+        const float n1 = fmaxf(m1, block_max(s1, scratch)), n2 = fmaxf(m2, block_max(s2, scratch));
+        const float p1 = s1 > -INFINITY ? expf(s1 - n1) : 0.f, p2 = s2 > -INFINITY ? expf(s2 - n2) : 0.f;
+        const float c1 = m1 == -INFINITY ? 0.f : expf(m1 - n1), c2 = m2 == -INFINITY ? 0.f : expf(m2 - n2);
+        l1 = l1 * c1 + block_sum(p1, scratch);
+        l2 = l2 * c2 + block_sum(p2, scratch);
+        m1 = n1; m2 = n2;
+        sp1[threadIdx.x] = p1;
+        sp2[threadIdx.x] = p2;
+        __syncthreads();
+        const int j_begin = max(0, lo - base), j_end = min(KT, hi - base);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int e = threadIdx.x + c * KT;
+            if (e >= vd) continue;
+            float x1 = a1[c] * c1, x2 = a2[c] * c2;
+            for (int jj = j_begin; jj < j_end; ++jj) {
+                const int key = base + jj;
+                const int page = bt[key / ps];
+                if (page < 0) continue;
+                const float v = to_f32(cache_values(pool, cache, page, kvh, key % ps)[e]);
+                x1 = fmaf(sp1[jj], v, x1);
+                x2 = fmaf(sp2[jj], v, x2);
+            }
+            a1[c] = x1; a2[c] = x2;
+        }
+        __syncthreads();
+    }
+    const float i1 = l1 > 0.f ? 1.f / l1 : 0.f, i2 = l2 > 0.f ? 1.f / l2 : 0.f;
+    float o[2], ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int e = threadIdx.x + c * KT;
+        o[c] = e < vd ? a1[c] * i1 - lambda * (a2[c] * i2) : 0.f;
+        ss += o[c] * o[c];
+    }
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)vd + eps) * out_scale;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int e = threadIdx.x + c * KT;
+        if (e < vd) out[((size_t)t * nh + h) * vd + e] = from_f32<T>(o[c] * r);
+    }
+}
+
+ST_EXPORT int st_diff_attention_plain(const void* q, const void* pool, long long page_stride, long long entry_offset,
+                                      void* out, const int* positions, const int* seq_of_token, const int* slots,
+                                      const int* block_table, int max_pages, int n_tokens, int nh, int nkv, int dim,
+                                      int vd, int page_size, float scale, float cap, int block, int window,
+                                      float lambda, float eps, float out_scale, int* status, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || dim <= 0 || vd <= 0 || page_size <= 0) return ST_ERR_BAD_ARG;
+    if (vd > 2 * KT || dim > 1024) return ST_ERR_TOO_LARGE;
+    const DiffCache c = {max_pages, page_size, nkv, 2 * dim, vd, page_stride, entry_offset};
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_tokens, nh);
+    const size_t smem = (size_t)(2 * dim + 2 * KT) * sizeof(float);
+    if (dtype == 0)
+        diff_attention_plain_kernel<float><<<grid, KT, smem, s>>>((const float*)q, (const float*)pool, c, (float*)out, positions,
+            seq_of_token, slots, block_table, nh, dim, scale, cap, block, window, lambda, eps, out_scale, status);
+    else if (dtype == 1)
+        diff_attention_plain_kernel<bf16><<<grid, KT, smem, s>>>((const bf16*)q, (const bf16*)pool, c, (bf16*)out, positions,
+            seq_of_token, slots, block_table, nh, dim, scale, cap, block, window, lambda, eps, out_scale, status);
+    else return ST_ERR_BAD_DTYPE;
+    return st_launch_status();
+}

@@ -17,7 +17,7 @@
 template <typename T, typename TO, bool VEC>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, const T* __restrict__ src,
                              int width, const int* __restrict__ pos, const T* __restrict__ pos_table,
-                             int pos_offset, TO* __restrict__ out) {
+                             int pos_offset, TO* __restrict__ out, float scale) {
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
     const int t = blockIdx.x;
@@ -30,12 +30,13 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     if (VEC) {
         for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
             float4 v = src ? load4_cg(row + e) : load4(row + e);
+            if (scale != 1.f) v = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
             if (prow) v = add4(v, load4(prow + e));
             store4(o + e, v);
         }
     } else {
         for (int e = threadIdx.x; e < width; e += blockDim.x) {
-            float v = src ? load1_cg(row + e) : to_f32(row[e]);
+            float v = (src ? load1_cg(row + e) : to_f32(row[e])) * scale;
             if (prow) v += to_f32(prow[e]);
             o[e] = from_f32<TO>(v);
         }
@@ -44,27 +45,28 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
 
 template <typename T, typename TO>
 static int launch_embed(const int* ids, const void* table, const void* src, int n_tokens, int width, const int* pos,
-                        const void* pos_table, int pos_offset, void* out, cudaStream_t s) {
+                        const void* pos_table, int pos_offset, void* out, cudaStream_t s, float scale = 1.f) {
     const bool vec = width % 4 == 0 && aligned16(table) && aligned16(src) && aligned16(pos_table) && aligned16(out);
     int block = vec ? (width / 4 + 31) / 32 * 32 : 256;
     if (block > 512) block = 512;
     if (block < 32) block = 32;
     if (vec)
         return st_launch_pdl("embed", embed_kernel<T, TO, true>, dim3(n_tokens), dim3(block), 0, s, ids, (const T*)table,
-                             (const T*)src, width, pos, (const T*)pos_table, pos_offset, (TO*)out);
+                             (const T*)src, width, pos, (const T*)pos_table, pos_offset, (TO*)out, scale);
     return st_launch_pdl("embed", embed_kernel<T, TO, false>, dim3(n_tokens), dim3(block), 0, s, ids, (const T*)table,
-                         (const T*)src, width, pos, (const T*)pos_table, pos_offset, (TO*)out);
+                         (const T*)src, width, pos, (const T*)pos_table, pos_offset, (TO*)out, scale);
 }
 
-// out[t] = table[ids[t]] (+ pos_table[pos[t] + pos_offset]);  out is float when out_f32, else the table's type
+// out[t] = scale * table[ids[t]] (+ pos_table[pos[t] + pos_offset]);  out is float when out_f32, else the table's type
 ST_EXPORT int st_embed(const int* ids, const void* table, int n_tokens, int width, const int* pos,
-                       const void* pos_table, int pos_offset, void* out, int dtype, int out_f32, void* stream) {
+                       const void* pos_table, int pos_offset, void* out, int dtype, int out_f32, float scale,
+                       void* stream) {
     if (n_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == 0) return launch_embed<float, float>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s);
+    if (dtype == 0) return launch_embed<float, float>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s, scale);
     if (dtype != 1) return ST_ERR_BAD_DTYPE;
-    if (out_f32) return launch_embed<bf16, float>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s);
-    return launch_embed<bf16, bf16>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s);
+    if (out_f32) return launch_embed<bf16, float>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s, scale);
+    return launch_embed<bf16, bf16>(ids, table, nullptr, n_tokens, width, pos, pos_table, pos_offset, out, s, scale);
 }
 
 // out[t] = in[t] + pos_table[pos[t] + pos_offset]   (used after a project_in product)

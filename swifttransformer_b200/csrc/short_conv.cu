@@ -1,0 +1,115 @@
+// Short causal convolutions over time, one filter per channel, with the last
+// taps-1 inputs of every request kept in a state slot so that a request may
+// arrive in portions cut anywhere.
+//
+//   y[t][c] = sum_j w[c][j] * u[t - taps + 1 + j][c]          (zeros before position 0)
+//
+// The state of a request holds the inputs at positions len-(taps-1) .. len-1
+// in that order (zero where the position is negative: a fresh slot is all
+// zeros, which is exactly "nothing before the sequence's start").
+//
+// Who may touch the state: within one launch the tokens of a request read the
+// old state while its new state has to be written.  `conv_residual` gives the
+// first token of a request in the step to the thread that also owns the
+// request's state for that channel: it computes the outputs of the first
+// taps-1 tokens itself (the only ones that read the state) and then writes the
+// new state; all other threads read the step's own rows only.  A kernel that
+// reads the state in many threads (the fused q/k/v preparation of
+// diff_attention.cu) leaves it unchanged and is followed by
+// `conv_state_update`, where one thread per (request, channel) reads all it
+// needs before it writes.
+#include "common.cuh"
+
+#define CONV_MAX_TAPS 8
+
+// out[t][c] = (residual ? in[t][c] : 0) + conv(in)[t][c];  in: float residual rows or activations
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+conv_residual_kernel(const TI* __restrict__ in, const float* __restrict__ w, float* __restrict__ state,
+                     TO* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                     const int* __restrict__ q_start, const int* __restrict__ slots, int channels, int taps,
+                     int residual) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.y;
+    if (c >= channels || positions[t] < 0) return;      // padding token of a fixed-shape step
+    const int b = seq_of_token[t];
+    const int first = q_start[b], n = q_start[b + 1] - first, i = t - first;
+    const int keep = taps - 1;
+    float wv[CONV_MAX_TAPS];
+    for (int j = 0; j < taps; ++j) wv[j] = w[(size_t)c * taps + j];
+    if (i >= keep) {
+        float y = 0.f;
+        for (int j = 0; j < taps; ++j) y = fmaf(wv[j], to_f32(in[(size_t)(t - keep + j) * channels + c]), y);
+        out[(size_t)t * channels + c] = from_f32<TO>((residual ? to_f32(in[(size_t)t * channels + c]) : 0.f) + y);
+        return;
+    }
+    if (i != 0) return;                                 // done by the thread of the request's first token
+    // u = old state followed by the first rows of the step: u[keep + k] is the step's token k
+    float* st = state + (size_t)slots[b] * keep * channels + c;
+    float u[2 * CONV_MAX_TAPS];
+    const int m = n < keep ? n : keep;                  // tokens that read the state
+    for (int j = 0; j < keep; ++j) u[j] = st[(size_t)j * channels];
+    for (int k = 0; k < m; ++k) u[keep + k] = to_f32(in[(size_t)(first + k) * channels + c]);
+    for (int k = 0; k < m; ++k) {
+        float y = 0.f;
+        for (int j = 0; j < taps; ++j) y = fmaf(wv[j], u[k + j], y);
+        out[(size_t)(first + k) * channels + c] = from_f32<TO>((residual ? u[keep + k] : 0.f) + y);
+    }
+    // the last `keep` inputs of old state + all n rows
+    for (int j = 0; j < keep; ++j) {
+        const int src = n + j;                          // index into (state, rows of the step)
+        st[(size_t)j * channels] = src < keep ? u[src] : to_f32(in[(size_t)(first + src - keep) * channels + c]);
+    }
+}
+
+// state <- the last taps-1 rows of (state, the request's rows of this step), for every request of the step
+template <typename TI>
+__global__ void __launch_bounds__(256)
+conv_state_update_kernel(const TI* __restrict__ in, int ld, float* __restrict__ state,
+                         const int* __restrict__ q_start, const int* __restrict__ slots, int channels, int taps) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    const int first = q_start[b], n = q_start[b + 1] - first;
+    if (c >= channels || n <= 0) return;                // a request without tokens: padding
+    const int keep = taps - 1;
+    float* st = state + (size_t)slots[b] * keep * channels + c;
+    float v[CONV_MAX_TAPS];
+    for (int j = 0; j < keep; ++j) {
+        const int src = n + j;
+        v[j] = src < keep ? st[(size_t)src * channels] : to_f32(in[(size_t)(first + src - keep) * ld + c]);
+    }
+    for (int j = 0; j < keep; ++j) st[(size_t)j * channels] = v[j];
+}
+
+// in: [n_tokens, channels] float (in_f32) or the storage type; out: [n_tokens, channels] storage type `dtype`
+ST_EXPORT int st_conv_residual(const void* in, int in_f32, const float* w, float* state, void* out,
+                               const int* positions, const int* seq_of_token, const int* q_start, const int* slots,
+                               int n_tokens, int channels, int taps, int residual, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (channels <= 0 || taps < 1) return ST_ERR_BAD_ARG;
+    if (taps > CONV_MAX_TAPS) return ST_ERR_TOO_LARGE;
+    if (dtype != 0 && dtype != 1) return ST_ERR_BAD_DTYPE;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((channels + 255) / 256, n_tokens);
+#define CONV_LAUNCH(TI, TO) conv_residual_kernel<TI, TO><<<grid, 256, 0, s>>>((const TI*)in, w, state, (TO*)out, positions, \
+        seq_of_token, q_start, slots, channels, taps, residual)
+    if (dtype == 0) CONV_LAUNCH(float, float);
+    else if (in_f32) CONV_LAUNCH(float, bf16);
+    else CONV_LAUNCH(bf16, bf16);
+#undef CONV_LAUNCH
+    return st_launch_status();
+}
+
+// in: [rows, ld] of which the first `channels` columns are the convolution's inputs
+ST_EXPORT int st_conv_state_update(const void* in, int ld, float* state, const int* q_start, const int* slots,
+                                   int n_seqs, int channels, int taps, int dtype, void* stream) {
+    if (n_seqs <= 0 || taps <= 1) return 0;
+    if (channels <= 0 || ld < channels) return ST_ERR_BAD_ARG;
+    if (taps > CONV_MAX_TAPS) return ST_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((channels + 255) / 256, n_seqs);
+    if (dtype == 0) conv_state_update_kernel<float><<<grid, 256, 0, s>>>((const float*)in, ld, state, q_start, slots, channels, taps);
+    else if (dtype == 1) conv_state_update_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, ld, state, q_start, slots, channels, taps);
+    else return ST_ERR_BAD_DTYPE;
+    return st_launch_status();
+}

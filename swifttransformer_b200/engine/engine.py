@@ -110,12 +110,21 @@ class LLMEngine:
         filled to the length limit would need."""
         from ..parts.base import PagedKVSpec, StateSpec
         esize = torch.empty((), dtype=self.model.dtype).element_size()
-        per_page = sum(2 * s.num_kv_heads * s.head_dim * cfg.page_size * esize
-                       for s in specs if isinstance(s, PagedKVSpec))
+        leaves = []
+
+        def walk(s):
+            if isinstance(s, (tuple, list)):
+                for sub in s:
+                    walk(sub)
+            else:
+                leaves.append(s)
+        walk(list(specs))
+        per_page = sum(s.num_kv_heads * (2 * s.head_dim if s.value_dim is None else s.head_dim + s.value_dim)
+                       * cfg.page_size * esize for s in leaves if isinstance(s, PagedKVSpec))
         if per_page == 0:
             return 1
         state_bytes = 0
-        for s in specs:
+        for s in leaves:
             if isinstance(s, StateSpec):
                 n = cfg.max_num_seqs * torch.empty((), dtype=s.dtype).element_size()
                 for k in s.shape:

@@ -21,7 +21,7 @@ from . import build as _build
 
 _LIB = None
 
-ACT_CODES = {"none": 0, "relu": 1, "gelu": 2}
+ACT_CODES = {"none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4}
 NORM_CODES = {"layernorm": 0, "rmsnorm": 1, "none": 2}
 
 _ERRORS = {-1: "unsupported dtype", -2: "unsupported size", -3: "size beyond the kernel's limit",
@@ -115,15 +115,15 @@ def sm_count(device=None) -> int:
 
 # ------------------------------------------------------------------ embedding
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, positions: Optional[torch.Tensor] = None,
-          pos_table: Optional[torch.Tensor] = None, pos_offset: int = 0) -> torch.Tensor:
-    """out[t] = table[ids[t]] (+ pos_table[positions[t] + pos_offset]); out is float32 or table's type."""
+          pos_table: Optional[torch.Tensor] = None, pos_offset: int = 0, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = scale * table[ids[t]] (+ pos_table[positions[t] + pos_offset]); out is float32 or table's type."""
     n, width = ids.numel(), table.shape[1]
     assert out.shape == (n, width) and out.is_contiguous() and table.is_contiguous()
     if pos_table is not None:
         assert pos_table.shape[1] == width and pos_table.dtype == table.dtype
     _check(lib().st_embed(_p(ids), _p(table), n, width, _p(positions) if pos_table is not None else None,
                           _p(pos_table), pos_offset, _p(out), _dt(table), int(out.dtype == torch.float32),
-                          _stream()), "embed")
+                          _f(scale), _stream()), "embed")
     return out
 
 
@@ -680,6 +680,116 @@ def attention_prefill(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torc
                                       _p(slots), _p(block_table), block_table.shape[1], n_layers, layer, nh, nkv,
                                       d, page_size, _f(scale), window, q_stride, _p(status), _stream()),
            "attention_prefill")
+    return out
+
+
+# ------------------------------------------------- short convolutions, gated units, output norms
+def conv_residual(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                  seq_of_token: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+                  residual: bool = True) -> torch.Tensor:
+    """out[t] = (x[t] if residual) + sum_j w[:, j] * x[t - taps + 1 + j] along each request's tokens, one filter per
+    channel.  x: [tokens, channels] float32 (the residual stream) or the type of ``out``; w: float32 [channels, taps];
+    state: float32 [slots, taps - 1, channels], a request's last taps - 1 inputs, read and moved on by this call."""
+    n, c = x.shape
+    taps = w.shape[1]
+    assert x.is_contiguous() and out.is_contiguous() and out.shape == x.shape and w.dtype == torch.float32
+    assert w.shape[0] == c and w.is_contiguous() and state.dtype == torch.float32
+    assert state.shape[1:] == (taps - 1, c) and state.is_contiguous()
+    assert x.dtype == torch.float32 or x.dtype == out.dtype
+    _check(lib().st_conv_residual(_p(x), int(x.dtype == torch.float32), _p(w), _p(state), _p(out), _p(positions),
+                                  _p(seq_of_token), _p(q_start), _p(slots), n, c, taps, int(residual), _dt(out),
+                                  _stream()), "conv_residual")
+    return out
+
+
+def conv_state_update(x: torch.Tensor, channels: int, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+                      n_seqs: int) -> None:
+    """state[slot] <- the last taps - 1 rows of (state[slot], the request's rows of x in this step), for every request
+    of the step; x: [tokens, >= channels] whose first ``channels`` columns are a convolution's inputs."""
+    assert x.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous() and state.shape[2] == channels
+    _check(lib().st_conv_state_update(_p(x), x.shape[1], _p(state), _p(q_start), _p(slots), n_seqs, channels,
+                                      state.shape[1] + 1, _dt(x), _stream()), "conv_state_update")
+
+
+def norm_add(x: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, mult: float, eps: float,
+             positions: Optional[torch.Tensor] = None, out_act: Optional[torch.Tensor] = None) -> None:
+    """x[r] += mult * gain * y[r] / sqrt(mean(y[r]^2) + eps) in place on the float32 residual rows; ``gain`` is one
+    float32 number on the device.  ``out_act``: also the new x in y's type.  Rows whose position is negative
+    (padding) are left alone."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
+    assert gain.dtype == torch.float32 and gain.numel() == 1
+    if out_act is not None:
+        assert out_act.dtype == y.dtype and out_act.shape == x.shape and out_act.is_contiguous()
+    _check(lib().st_norm_add(_p(x), _p(y), _p(gain), _f(mult), _f(eps), x.shape[0], x.shape[1], _p(positions),
+                             _p(out_act), _dt(y), _stream()), "norm_add")
+
+
+def gated_act(gu: torch.Tensor, act: str) -> torch.Tensor:
+    """act(gu[:, :inner]) * gu[:, inner:] for the fused gate | up product gu [rows, 2 * inner]."""
+    assert gu.is_contiguous() and gu.shape[1] % 2 == 0
+    inner = gu.shape[1] // 2
+    out = torch.empty((gu.shape[0], inner), dtype=gu.dtype, device=gu.device)
+    _check(lib().st_gated_act(_p(gu), _p(out), gu.shape[0], inner, ACT_CODES[act], _dt(gu), _stream()), "gated_act")
+    return out
+
+
+# ------------------------------------------------------------ differential attention
+def _flat_pool(pool: torch.Tensor, layer: int, nkv: int, dim: int, vd: int, page_size: int):
+    """(page stride, offset of the entry) in elements, for a pool [pages, entries, nkv * page_size * (2 dim + vd)]."""
+    assert pool.dim() == 3 and pool.is_contiguous() and pool.shape[2] == nkv * page_size * (2 * dim + vd)
+    return ctypes.c_longlong(pool.stride(0)), ctypes.c_longlong(layer * pool.stride(1))
+
+
+def diff_qkv_prepare(proj: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor, q_norm: torch.Tensor,
+                     k_norm: torch.Tensor, eps: float, inv_freq: torch.Tensor, rot_dims: int, q_out: torch.Tensor,
+                     pool: torch.Tensor, layer: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                     q_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int,
+                     dim: int, vd: int, page_size: int, status: torch.Tensor, write_kv: bool = True) -> None:
+    """From the fused projection q | k | v of the step's tokens: the short convolution over time of every channel
+    (reading, not moving, the requests' last inputs in ``conv_state``), RMS norm of each map of each query and key
+    head with the shared weights, rotation of the first ``rot_dims`` dimensions in neighbouring pairs by
+    position * inv_freq, queries to ``q_out`` [tokens, nh * 2 * dim], keys and values into their pages."""
+    taps = conv_w.shape[1]
+    channels = (nh + nkv) * 2 * dim + nkv * vd
+    assert proj.is_contiguous() and proj.shape[1] == channels and conv_w.shape == (channels, taps)
+    assert conv_state.shape[1:] == (taps - 1, channels) and pool.dtype == proj.dtype == q_out.dtype
+    stride, offset = _flat_pool(pool, layer, nkv, dim, vd, page_size)
+    _check(lib().st_diff_qkv_prepare(_p(proj), proj.shape[1], _p(conv_w), _p(conv_state), taps, _p(q_norm), _p(k_norm),
+                                     _f(eps), _p(inv_freq), rot_dims, _p(q_out), _p(pool), stride, offset,
+                                     _p(positions), _p(seq_of_token), _p(q_start), _p(slots), _p(block_table),
+                                     block_table.shape[1], proj.shape[0], nh, nkv, dim, vd, page_size, int(write_kv),
+                                     _p(status), _dt(proj), _stream()), "diff_qkv_prepare")
+
+
+def diff_attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
+                         seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
+                         nkv: int, dim: int, vd: int, page_size: int, scale: float, cap: float, block: int,
+                         window: int, lam: float, eps: float, out_scale: float,
+                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Differential attention of the step's queries q [tokens, nh * 2 * dim] over the paged cache, one block per
+    (token, head), float arithmetic for either type: out [tokens, nh * vd] =
+    rms(softmax(cap(q1 k1)) V - lam * softmax(cap(q2 k2)) V) * out_scale."""
+    stride, offset = _flat_pool(pool, layer, nkv, dim, vd, page_size)
+    _check(lib().st_diff_attention_plain(_p(q), _p(pool), stride, offset, _p(out), _p(positions), _p(seq_of_token),
+                                         _p(slots), _p(block_table), block_table.shape[1], q.shape[0], nh, nkv, dim,
+                                         vd, page_size, _f(scale), _f(cap), block, window, _f(lam), _f(eps),
+                                         _f(out_scale), _p(status), _dt(q), _stream()), "diff_attention_plain")
+    return out
+
+
+# ------------------------------------------------------------ gated linear recurrence
+def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor, lower: torch.Tensor,
+               norm_w: torch.Tensor, eps: float, state: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+               slots: torch.Tensor, n_seqs: int, nh: int, dim: int, vd: int) -> torch.Tensor:
+    """The HGRN2 recurrence over each request's tokens of the step, from the fused projection (queries, gates and
+    values at column offsets q_off, f_off, v_off): S <- diag(f) S + (1 - f) v^T, o = S^T silu(q), f = lower +
+    (1 - lower) sigmoid(gate + f_bias); out [tokens, nh * vd] = rms(o) * norm_w per head.  ``state``: float32
+    [slots, nh, dim, vd], read and moved on."""
+    assert proj.is_contiguous() and out.is_contiguous() and out.shape == (proj.shape[0], nh * vd)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (nh, dim, vd)
+    _check(lib().st_hgrn2_scan(_p(proj), proj.shape[1], q_off, f_off, v_off, _p(f_bias), _p(lower), _p(norm_w),
+                               _f(eps), _p(state), _p(out), _p(q_start), _p(slots), n_seqs, nh, dim, vd, _dt(proj),
+                               _stream()), "hgrn2_scan")
     return out
 
 

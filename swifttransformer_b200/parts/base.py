@@ -15,7 +15,7 @@ order is written out in src/csrc/model/gpt/gpt.cc:304-503.
 
 Interfaces
 ----------
-Mixer.cache_spec()        -> PagedKVSpec | StateSpec | None
+Mixer.cache_spec()        -> PagedKVSpec | StateSpec | None | a tuple of these (the layer step then gets a tuple of views)
 Mixer.step_plan()         -> StepPlan | None  (host work once per step, see StepPlan)
 Mixer.forward(h, ctx, cache) -> Delta         h: [N, width] activations
 FeedForward.forward(h, ctx)  -> Delta
@@ -52,10 +52,20 @@ class Delta:
 
 @dataclasses.dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values per token, kept in pages.  ``window`` None: all keys stay."""
+    """Keys and values per token, kept in pages.  ``window`` None: all keys stay.
+
+    ``value_dim``: the size of a value row when it differs in kind from a key row of ``head_dim`` (a mixer
+    whose keys and values have sizes of their own).  The group's pool is then a flat tensor
+    [pages, entries, kv_heads * page_size * (head_dim + value_dim)] in which an entry's part of a page holds
+    the keys [kv_head][position][head_dim] followed by the values [kv_head][position][value_dim]; with
+    ``value_dim`` None it is [pages, entries, 2, kv_heads, page_size, head_dim].
+    ``block``: the mask is block-diagonal, a query sees only the keys of its own block of ``block``
+    positions (counted from position 0): pages that lie before the block of the next query are given back."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+    block: Optional[int] = None
 
 
 @dataclasses.dataclass(frozen=True)

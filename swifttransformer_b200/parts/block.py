@@ -5,6 +5,8 @@ pre_norm  (OPT with do_layer_norm_before; src/csrc/model/gpt/gpt.cc:304-503):
     r = x + mixer(norm1(x));  x' = r + ffn(norm2(r))
 post_norm (do_layer_norm_before false; the reference refuses it, gpt.cc:238-240):
     r = norm1(x + mixer(x));  x' = norm2(r + ffn(r))
+norm_after (the norm on the sub-layer's output only; the sub-layers read x itself):
+    r = x + mult * norm1(mixer(x));  x' = r + mult * norm2(ffn(r))
 
 The residual stream is float32 for every storage type.  A block leaves the
 feed-forward's result as ``pending``: the next norm kernel (of the next block
@@ -88,4 +90,47 @@ class PostNormBlock(Block):
         h = self.norm1.apply(stream.x, a, act_dtype=stream.act_dtype, normalise_residual=True)
         f = self.feed_forward.forward(h, ctx)
         stream.act = self.norm2.apply(stream.x, f, act_dtype=stream.act_dtype, normalise_residual=True)
+        stream.pending = None
+
+
+@BLOCKS.register("norm_after")
+class NormAfterBlock(Block):
+    """x <- x + mult * norm1(mixer(x)); x <- x + mult * norm2(ffn(x)).  The norms are ``rmsnorm_scalar`` parts (one
+    gain each); ``mult`` scales what is added to the residual stream.  The feed-forward may be absent (None).
+    The sums and the norms' statistics are float; one kernel per sub-layer normalises its output, adds it to the
+    residual rows in place and hands the new rows on in the activation type.  A mixer that declares
+    ``reads_residual`` gets the float rows themselves instead of a copy in the activation type."""
+
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], norm1: Norm, norm2: Optional[Norm],
+                 mult: float = 1.0):
+        if (feed_forward is None) != (norm2 is None):
+            raise ValueError("a block has a second norm exactly when it has a feed-forward")
+        for n in (norm1, norm2):
+            if n is not None and not hasattr(n, "gain"):
+                raise ValueError("norm_after takes norms with a single gain (rmsnorm_scalar)")
+        super().__init__(mixer, feed_forward, norm1, norm2)
+        self.mult = float(mult)
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
+        x = stream.x
+        if stream.pending is not None:
+            stream.materialise()
+        if getattr(self.mixer, "reads_residual", False):
+            h = x
+        else:
+            h = stream.materialise()
+        a = self.mixer.forward(h, ctx, cache)
+        assert a.bias is None and a.parts is None
+        act = None
+        if self.feed_forward is not None and stream.act_dtype != torch.float32:
+            act = torch.empty(x.shape, dtype=stream.act_dtype, device=x.device)
+        ops.norm_add(x, a.value, self.norm1.gain, self.mult, self.norm1.eps, ctx.positions, out_act=act)
+        stream.act = None
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(act if act is not None else x, ctx)
+            assert f.bias is None and f.parts is None
+            ops.norm_add(x, f.value, self.norm2.gain, self.mult, self.norm2.eps, ctx.positions)
         stream.pending = None

@@ -21,8 +21,9 @@ from .position import PositionEncoding
 
 class Embedding(Part):
     def __init__(self, vocab: int, embed_width: int, hidden: int, table_name: str,
-                 project_in_name: Optional[str] = None):
+                 project_in_name: Optional[str] = None, scale: float = 1.0):
         self.vocab, self.embed_width, self.hidden = vocab, embed_width, hidden
+        self.scale = float(scale)      # the looked-up row is multiplied by this
         self.table_name, self.project_in_name = table_name, project_in_name
         self.table: Optional[torch.Tensor] = None
         self.project_in: Optional[torch.Tensor] = None
@@ -48,12 +49,12 @@ class Embedding(Part):
         tab = position.hidden_table()
         if self.project_in is None:
             if tab is not None:
-                ops.embed(ids, self.table, x, positions, tab[0], tab[1])
+                ops.embed(ids, self.table, x, positions, tab[0], tab[1], scale=self.scale)
             else:
-                ops.embed(ids, self.table, x)
+                ops.embed(ids, self.table, x, scale=self.scale)
             return x
         e = torch.empty((n, self.embed_width), dtype=self.table.dtype, device=dev)
-        ops.embed(ids, self.table, e)
+        ops.embed(ids, self.table, e, scale=self.scale)
         h = ops.linear(e, self.project_in)
         if tab is not None:
             ops.add_positions(h, positions, tab[0], tab[1], x)

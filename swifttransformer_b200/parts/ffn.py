@@ -6,7 +6,7 @@ bias travels with the result so the next norm kernel adds it with the residual.
 """
 from __future__ import annotations
 
-from typing import Any, Dict, List
+from typing import Any, Dict, List, Optional
 
 import torch
 
@@ -65,3 +65,32 @@ class DenseFFN(FeedForward):
 
     def param_bytes(self) -> int:
         return (self.w1.numel() + self.w2.numel()) * self.w1.element_size()
+
+
+@FEED_FORWARDS.register("gated")
+class GatedFFN(FeedForward):
+    """z = down(act(gate h) * (up h)), no biases.  The gate and up matrices are stacked at load time so that one
+    product gives both; ``activation`` is any of ops.ACT_CODES (the tanh form of GELU, SiLU, ...)."""
+
+    def __init__(self, hidden: int, inner: int, activation: str, gate_name: str, up_name: str, down_name: str):
+        if activation not in ops.ACT_CODES:
+            raise ValueError(f"activation '{activation}' is not supported ({', '.join(ops.ACT_CODES)})")
+        self.hidden, self.inner, self.activation = hidden, inner, activation
+        self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
+        self.w_gu = self.w_down = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec(self.gate_name, (self.inner, self.hidden), MATRIX),
+                ParamSpec(self.up_name, (self.inner, self.hidden), MATRIX),
+                ParamSpec(self.down_name, (self.hidden, self.inner), MATRIX)]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_gu = torch.cat([tensors.pop(self.gate_name), tensors.pop(self.up_name)], dim=0).contiguous()
+        self.w_down = tensors[self.down_name]
+
+    def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
+        u = ops.gated_act(ops.linear(h, self.w_gu), self.activation)
+        return Delta(ops.linear(u, self.w_down))
+
+    def param_bytes(self) -> int:
+        return (self.w_gu.numel() + self.w_down.numel()) * self.w_gu.element_size()

@@ -82,6 +82,30 @@ class RMSNorm(Norm):
         return 4 * self.width if self.affine else 0
 
 
+@NORMS.register("rmsnorm_scalar")
+class ScalarRMSNorm(Norm):
+    """RMS norm whose gain is one number for all coordinates: y = g * x / sqrt(mean(x^2) + eps).  The tensor of
+    that name holds the single number (shape [] or [1]).  ``apply`` goes through the kernel of the other norms with
+    the number spread over the width; a block that normalises a sub-layer's output before the residual sum reads
+    ``gain`` (the number on the device) for ``ops.norm_add``."""
+    kind = "rmsnorm"
+
+    def __init__(self, width: int, eps: float = 1e-5, affine: bool = True, prefix: str = "", name: str = ""):
+        super().__init__(width, eps, affine, prefix)
+        self.name = name or prefix
+        self.gain: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec(self.name, (), GAIN)]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.gain = tensors[self.name].reshape(1).to(torch.float32).contiguous()
+        self.gamma = self.gain.expand(self.width).contiguous()
+
+    def param_bytes(self) -> int:
+        return 4
+
+
 @NORMS.register("none")
 class NoNorm(Norm):
     """Residual add and cast only."""

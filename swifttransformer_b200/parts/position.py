@@ -11,6 +11,7 @@ keys go to the cache.
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -59,3 +60,25 @@ class LearnedPositions(PositionEncoding):
 
     def add_to(self, x: torch.Tensor, positions: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return ops.add_positions(x, positions, self.table, self.offset, out)
+
+
+@POSITION_ENCODINGS.register("rotary_pairs")
+class RotaryPairs(PositionEncoding):
+    """Rotation of queries and keys by position: of the first ``dims`` dimensions of a head, dimension 2i is paired
+    with 2i+1 (neighbours, not halves) and the pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a)
+    with a = p * base^(-2i/dims); the other dimensions pass unchanged.  The frequencies are computed once in double
+    precision and kept as float32; the angle and its sine and cosine are float32 in the kernels.  A mixer that
+    prepares its queries and keys in a kernel of its own takes ``inv_freq`` and ``dims`` from here."""
+
+    def __init__(self, dims: int, base: float, **_):
+        if dims < 0 or dims % 2:
+            raise ValueError(f"rotary dimensions must be even and not negative, got {dims}")
+        self.dims, self.base = int(dims), float(base)
+        self._tables: Dict[torch.device, torch.Tensor] = {}
+
+    def inv_freq(self, device) -> torch.Tensor:
+        device = torch.device(device)
+        if device not in self._tables:
+            f = [math.pow(self.base, -2.0 * i / self.dims) for i in range(self.dims // 2)] or [0.0]
+            self._tables[device] = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
+        return self._tables[device]

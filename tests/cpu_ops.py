@@ -22,8 +22,8 @@ def _act(y, act):
     return y
 
 
-def embed(ids, table, out, positions=None, pos_table=None, pos_offset=0):
-    v = table[ids.long()].double()
+def embed(ids, table, out, positions=None, pos_table=None, pos_offset=0, scale=1.0):
+    v = table[ids.long()].double() * scale
     if pos_table is not None:
         live = (positions >= 0).unsqueeze(1)       # padding tokens (position -1) get no position row
         v = v + pos_table[(positions.long() + pos_offset).clamp(min=0)].double() * live
