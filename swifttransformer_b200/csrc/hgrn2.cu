@@ -20,11 +20,13 @@ __global__ void __launch_bounds__(1024)
 hgrn2_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int v_off,
                   const float* __restrict__ f_bias, const float* __restrict__ lower,
                   const float* __restrict__ norm_w, float eps, float* __restrict__ state, T* __restrict__ out,
-                  const int* __restrict__ q_start, const int* __restrict__ slots, int nh, int dim, int vd) {
+                  const int* __restrict__ positions, const int* __restrict__ q_start,
+                  const int* __restrict__ slots, int nh, int dim, int vd) {
     extern __shared__ float smem[];
     const int b = blockIdx.x, h = blockIdx.y;
     const int first = q_start[b], n = q_start[b + 1] - first;
-    if (n <= 0) return;                                   // a request without tokens: padding
+    // padding of a fixed-shape step: a request without tokens, or one whose tokens stand at position -1
+    if (n <= 0 || positions[first] < 0) return;
     float* S = smem;                                      // [dim][vd]
     float* sq = S + (size_t)dim * vd;                     // [GROUP][dim]
     float* sf = sq + HG_GROUP * dim;                      // [GROUP][dim]
@@ -87,8 +89,8 @@ static size_t hgrn2_smem(int dim, int vd) {
 // state: [slots, nh, dim, vd] float; out: [tokens, nh * vd]
 ST_EXPORT int st_hgrn2_scan(const void* proj, int ld, int q_off, int f_off, int v_off, const float* f_bias,
                             const float* lower, const float* norm_w, float eps, float* state, void* out,
-                            const int* q_start, const int* slots, int n_seqs, int nh, int dim, int vd, int dtype,
-                            void* stream) {
+                            const int* positions, const int* q_start, const int* slots, int n_seqs, int nh, int dim,
+                            int vd, int dtype, void* stream) {
     if (n_seqs <= 0) return 0;
     if (nh <= 0 || dim <= 0 || vd <= 0) return ST_ERR_BAD_ARG;
     const size_t smem = hgrn2_smem(dim, vd);
@@ -106,7 +108,7 @@ ST_EXPORT int st_hgrn2_scan(const void* proj, int ld, int q_off, int f_off, int 
             if (e != cudaSuccess) return (int)e;                                                                      \
         }                                                                                                             \
         hgrn2_scan_kernel<T><<<grid, threads, smem, s>>>((const T*)proj, ld, q_off, f_off, v_off, f_bias, lower,      \
-                                                         norm_w, eps, state, (T*)out, q_start, slots, nh, dim, vd);  \
+                                                         norm_w, eps, state, (T*)out, positions, q_start, slots, nh, dim, vd); \
     } while (0)
     if (dtype == 0) HG_LAUNCH(float);
     else if (dtype == 1) HG_LAUNCH(bf16);

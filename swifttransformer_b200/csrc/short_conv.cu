@@ -29,8 +29,8 @@ conv_residual_kernel(const TI* __restrict__ in, const float* __restrict__ w, flo
                      TO* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                      const int* __restrict__ q_start, const int* __restrict__ slots, int channels, int taps,
                      int residual) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    const int t = blockIdx.y;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x;
     if (c >= channels || positions[t] < 0) return;      // padding token of a fixed-shape step
     const int b = seq_of_token[t];
     const int first = q_start[b], n = q_start[b + 1] - first, i = t - first;
@@ -66,11 +66,13 @@ conv_residual_kernel(const TI* __restrict__ in, const float* __restrict__ w, flo
 template <typename TI>
 __global__ void __launch_bounds__(256)
 conv_state_update_kernel(const TI* __restrict__ in, int ld, float* __restrict__ state,
-                         const int* __restrict__ q_start, const int* __restrict__ slots, int channels, int taps) {
+                         const int* __restrict__ positions, const int* __restrict__ q_start,
+                         const int* __restrict__ slots, int channels, int taps) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int b = blockIdx.y;
     const int first = q_start[b], n = q_start[b + 1] - first;
-    if (c >= channels || n <= 0) return;                // a request without tokens: padding
+    // padding of a fixed-shape step: a request without tokens, or one whose tokens stand at position -1
+    if (c >= channels || n <= 0 || positions[first] < 0) return;
     const int keep = taps - 1;
     float* st = state + (size_t)slots[b] * keep * channels + c;
     float v[CONV_MAX_TAPS];
@@ -90,7 +92,7 @@ ST_EXPORT int st_conv_residual(const void* in, int in_f32, const float* w, float
     if (taps > CONV_MAX_TAPS) return ST_ERR_TOO_LARGE;
     if (dtype != 0 && dtype != 1) return ST_ERR_BAD_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((channels + 255) / 256, n_tokens);
+    dim3 grid(n_tokens, (channels + 255) / 256);
 #define CONV_LAUNCH(TI, TO) conv_residual_kernel<TI, TO><<<grid, 256, 0, s>>>((const TI*)in, w, state, (TO*)out, positions, \
         seq_of_token, q_start, slots, channels, taps, residual)
     if (dtype == 0) CONV_LAUNCH(float, float);
@@ -101,15 +103,15 @@ ST_EXPORT int st_conv_residual(const void* in, int in_f32, const float* w, float
 }
 
 // in: [rows, ld] of which the first `channels` columns are the convolution's inputs
-ST_EXPORT int st_conv_state_update(const void* in, int ld, float* state, const int* q_start, const int* slots,
-                                   int n_seqs, int channels, int taps, int dtype, void* stream) {
+ST_EXPORT int st_conv_state_update(const void* in, int ld, float* state, const int* positions, const int* q_start,
+                                   const int* slots, int n_seqs, int channels, int taps, int dtype, void* stream) {
     if (n_seqs <= 0 || taps <= 1) return 0;
     if (channels <= 0 || ld < channels) return ST_ERR_BAD_ARG;
     if (taps > CONV_MAX_TAPS) return ST_ERR_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid((channels + 255) / 256, n_seqs);
-    if (dtype == 0) conv_state_update_kernel<float><<<grid, 256, 0, s>>>((const float*)in, ld, state, q_start, slots, channels, taps);
-    else if (dtype == 1) conv_state_update_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, ld, state, q_start, slots, channels, taps);
+    if (dtype == 0) conv_state_update_kernel<float><<<grid, 256, 0, s>>>((const float*)in, ld, state, positions, q_start, slots, channels, taps);
+    else if (dtype == 1) conv_state_update_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, ld, state, positions, q_start, slots, channels, taps);
     else return ST_ERR_BAD_DTYPE;
     return st_launch_status();
 }

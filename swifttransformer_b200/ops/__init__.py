@@ -702,12 +702,12 @@ def conv_residual(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, out: to
     return out
 
 
-def conv_state_update(x: torch.Tensor, channels: int, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
-                      n_seqs: int) -> None:
+def conv_state_update(x: torch.Tensor, channels: int, state: torch.Tensor, positions: torch.Tensor,
+                      q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int) -> None:
     """state[slot] <- the last taps - 1 rows of (state[slot], the request's rows of x in this step), for every request
     of the step; x: [tokens, >= channels] whose first ``channels`` columns are a convolution's inputs."""
     assert x.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous() and state.shape[2] == channels
-    _check(lib().st_conv_state_update(_p(x), x.shape[1], _p(state), _p(q_start), _p(slots), n_seqs, channels,
+    _check(lib().st_conv_state_update(_p(x), x.shape[1], _p(state), _p(positions), _p(q_start), _p(slots), n_seqs, channels,
                                       state.shape[1] + 1, _dt(x), _stream()), "conv_state_update")
 
 
@@ -779,8 +779,8 @@ def diff_attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: t
 
 # ------------------------------------------------------------ gated linear recurrence
 def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor, lower: torch.Tensor,
-               norm_w: torch.Tensor, eps: float, state: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
-               slots: torch.Tensor, n_seqs: int, nh: int, dim: int, vd: int) -> torch.Tensor:
+               norm_w: torch.Tensor, eps: float, state: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+               q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, nh: int, dim: int, vd: int) -> torch.Tensor:
     """The HGRN2 recurrence over each request's tokens of the step, from the fused projection (queries, gates and
     values at column offsets q_off, f_off, v_off): S <- diag(f) S + (1 - f) v^T, o = S^T silu(q), f = lower +
     (1 - lower) sigmoid(gate + f_bias); out [tokens, nh * vd] = rms(o) * norm_w per head.  ``state``: float32
@@ -788,7 +788,7 @@ def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: t
     assert proj.is_contiguous() and out.is_contiguous() and out.shape == (proj.shape[0], nh * vd)
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (nh, dim, vd)
     _check(lib().st_hgrn2_scan(_p(proj), proj.shape[1], q_off, f_off, v_off, _p(f_bias), _p(lower), _p(norm_w),
-                               _f(eps), _p(state), _p(out), _p(q_start), _p(slots), n_seqs, nh, dim, vd, _dt(proj),
+                               _f(eps), _p(state), _p(out), _p(positions), _p(q_start), _p(slots), n_seqs, nh, dim, vd, _dt(proj),
                                _stream()), "hgrn2_scan")
     return out
 

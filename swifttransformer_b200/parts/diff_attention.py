@@ -84,7 +84,8 @@ class DifferentialAttention(Mixer):
                              kv.block_table, self.nh, self.nkv, self.dim, self.vdim, kv.page_size, ctx.status,
                              write_kv=kv.writable)
         if self.taps > 1 and tails.writable:
-            ops.conv_state_update(proj, self.qw + self.kw + self.vw, tails.state, ctx.q_start, ctx.slots, ctx.n_seqs)
+            ops.conv_state_update(proj, self.qw + self.kw + self.vw, tails.state, ctx.positions, ctx.q_start, ctx.slots,
+                                  ctx.n_seqs)
         o = torch.empty((n, self.nh * self.vdim), dtype=h.dtype, device=h.device)
         ops.diff_attention_plain(q, kv.pool, kv.layer, o, ctx.positions, ctx.seq_of_token, ctx.slots, kv.block_table,
                                  self.nh, self.nkv, self.dim, self.vdim, kv.page_size, self.scale, self.softcap,
