@@ -115,55 +115,64 @@ def diff_lambda(w, p, diff):
 
 def differential_attention(h, w, p, mx, eps):
     """h [T, width] -> [T, width]; p is the tensor prefix '<layer>.mix.', mx the mixer's sizes and constants."""
-    T = h.shape[0]
-    H, G, d, dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
-    q = h @ w[p + "q"].T
-    k = h @ w[p + "k"].T
-    v = h @ w[p + "v"].T
-    q = causal_conv(q, w[p + "q.conv"])
-    k = causal_conv(k, w[p + "k.conv"])
-    v = causal_conv(v, w[p + "v.conv"])
-    q = q.reshape(T, H, 2, d)
-    k = k.reshape(T, G, 2, d)
+    q = causal_conv(h @ w[p + "q"].T, w[p + "q.conv"])
+    k = causal_conv(h @ w[p + "k"].T, w[p + "k.conv"])
+    v = causal_conv(h @ w[p + "v"].T, w[p + "v.conv"])
+    rot = mx.get("rot") or {"dims": 0, "base": 1.0}
+    out = attend_two_maps(q, k, v, mx["heads"], mx.get("kv_heads", mx["heads"]), mx["dim"], mx["vdim"],
+                          w[p + "q.norm"], w[p + "k.norm"], eps, rot["dims"], rot["base"], mx["scale"],
+                          mx.get("softcap", 0.0), mx["mask"]["size"] if mx.get("mask") else None,
+                          diff_lambda(w, p, mx["diff"]), 1.0 - mx["diff"])
+    return out @ w[p + "o"].T
+
+
+def attend_two_maps(q, k, v, H, G, d, dv, q_norm, k_norm, eps, rot_dims, rot_base, scale, cap, block, lam, out_scale):
+    """q [T, H*2*d], k [T, G*2*d], v [T, G*dv] after their convolutions -> [T, H*dv]: norm and rotation of the
+    queries and keys, the two capped softmax maps per head over the keys of the query's block, their difference,
+    the RMS norm of each head's result."""
+    T = q.shape[0]
+    q = rms(q.reshape(T, H, 2, d), eps) * q_norm
+    k = rms(k.reshape(T, G, 2, d), eps) * k_norm
     v = v.reshape(T, G, dv)
-    q = rms(q, eps) * w[p + "q.norm"]
-    k = rms(k, eps) * w[p + "k.norm"]
     pos = np.arange(T)
-    q = rotate_pairs(q, pos, mx["rot"]["dims"], mx["rot"]["base"])
-    k = rotate_pairs(k, pos, mx["rot"]["dims"], mx["rot"]["base"])
-    lam = diff_lambda(w, p, mx["diff"])
-    cap, scale, size = mx["softcap"], mx["scale"], mx["mask"]["size"]
+    if rot_dims:
+        q = rotate_pairs(q, pos, rot_dims, rot_base)
+        k = rotate_pairs(k, pos, rot_dims, rot_base)
     out = np.zeros((T, H, dv))
     for t in range(T):
-        lo = (t // size) * size
+        lo = (t // block) * block if block else 0
         for hd in range(H):
             g = hd // (H // G)
             maps = []
             for a in range(2):
                 s = (k[lo:t + 1, g, a] @ q[t, hd, a]) * scale
-                s = cap * np.tanh(s / cap)
+                if cap:
+                    s = cap * np.tanh(s / cap)
                 e = np.exp(s - s.max())
                 maps.append((e / e.sum()) @ v[lo:t + 1, g])
-            o = maps[0] - lam * maps[1]
-            out[t, hd] = rms(o, eps) * (1.0 - mx["diff"])
-    return out.reshape(T, H * dv) @ w[p + "o"].T
+            out[t, hd] = rms(maps[0] - lam * maps[1], eps) * out_scale
+    return out.reshape(T, H * dv)
 
 
-def hgrn2(h, w, p, mx, eps, state=None):
+def hgrn2(h, w, p, mx, eps):
     """h [T, width] -> [T, width]; the state S [heads, dim, vdim] starts at zero."""
-    T = h.shape[0]
-    H, d, dv = mx["heads"], mx["dim"], mx["vdim"]
-    q = silu(h @ w[p + "q"].T).reshape(T, H, d)
-    v = (h @ w[p + "v"].T).reshape(T, H, dv)
-    low = w[p + "lower"]
-    f = (low + (1.0 - low) * sigmoid(h @ w[p + "f"].T + w[p + "f.b"])).reshape(T, H, d)
-    S = np.zeros((H, d, dv)) if state is None else state
+    out = gated_recurrence(h @ w[p + "q"].T, h @ w[p + "f"].T, h @ w[p + "v"].T, w[p + "f.b"], w[p + "lower"],
+                           w[p + "norm"], mx["heads"], mx["dim"], mx["vdim"], eps)
+    return out @ w[p + "o"].T
+
+
+def gated_recurrence(zq, zf, v, f_bias, lower, norm_w, H, d, dv, eps):
+    """zq, zf [T, H*d], v [T, H*dv] (the three projections) -> [T, H*dv]."""
+    T = zq.shape[0]
+    q = silu(zq).reshape(T, H, d)
+    v = v.reshape(T, H, dv)
+    f = (lower + (1.0 - lower) * sigmoid(zf + f_bias)).reshape(T, H, d)
+    S = np.zeros((H, d, dv))
     out = np.zeros((T, H, dv))
     for t in range(T):
         S = f[t][:, :, None] * S + (1.0 - f[t])[:, :, None] * v[t][:, None, :]
         out[t] = np.einsum("hdv,hd->hv", S, q[t])
-    out = rms(out, eps) * w[p + "norm"]
-    return out.reshape(T, H * dv) @ w[p + "o"].T
+    return (rms(out, eps) * norm_w).reshape(T, H * dv)
 
 
 def feed_forward(h, w, p):
@@ -176,12 +185,12 @@ def feed_forward(h, w, p):
 
 def forward(cfg, w, tokens, return_layers=False):
     """Logits [T, vocab] for one whole sequence (and the residual stream after every layer)."""
-    eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
-    x = w["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
+    eps, m = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
+    x = w["embed"][np.asarray(tokens)] * cfg.get("embedding", {}).get("scale", 1.0)
     layers = []
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
-        h = x + causal_conv(x, w[p + "canon1"])
+        h = x + causal_conv(x, w[p + "canon1"]) if cfg.get("canon") else x
         if layer["type"] == "attention":
             y = differential_attention(h, w, p + "mix.", layer["mixer"], eps)
         elif layer["type"] == "hgrn2":
