@@ -19,26 +19,10 @@
 // shared weight, rotation of pairs of dimensions by position, cache write) and the plain attention kernel
 // (float arithmetic for either storage type, key tiles aligned to absolute positions: a row's result does not
 // depend on how the request was cut into steps or on what else is in the batch).
-#include "common.cuh"
+#include "diff_attention.cuh"
 
 #define CONV_MAX_TAPS 8
 #define PREP_THREADS 256
-
-struct DiffCache {
-    int max_pages, page_size, nkv, kd, vd;
-    long long page_stride;      // elements between consecutive pages of this entry
-    long long entry_offset;     // elements from the pool's start to this entry's part of page 0
-};
-
-template <typename T>
-__device__ __forceinline__ T* cache_keys(T* pool, const DiffCache& c, int page, int kvh, int pip) {
-    return pool + c.entry_offset + (long long)page * c.page_stride + ((long long)kvh * c.page_size + pip) * c.kd;
-}
-template <typename T>
-__device__ __forceinline__ T* cache_values(T* pool, const DiffCache& c, int page, int kvh, int pip) {
-    return pool + c.entry_offset + (long long)page * c.page_stride + (long long)c.nkv * c.page_size * c.kd +
-           ((long long)kvh * c.page_size + pip) * c.vd;
-}
 
 // One warp per unit of a token: a unit is one map of one query head (dim channels), one map of one key head
 // (dim channels) or one value head (vd channels).  A lane owns pairs of neighbouring channels, so that a
@@ -158,21 +142,14 @@ ST_EXPORT int st_diff_qkv_prepare(const void* proj, int ld, const float* conv_w,
 }
 
 // ------------------------------------------------------------------------------------------------
-// Plain differential attention: one block per (query token, head).
+// Plain differential attention: one block per (query token, head); `items` lists the tokens to serve
+// (n_tokens of them, -1: none), or is null for tokens 0..n_tokens-1.
 #define KT 128   // keys per tile == threads per block
-
-__device__ __forceinline__ int first_visible(int pos, int block, int window) {
-    if (block > 0) return (pos / block) * block;
-    if (window > 0) return max(0, pos - window + 1);
-    return 0;
-}
-
-__device__ __forceinline__ float soft_cap(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
 
 template <typename T>
 __global__ void __launch_bounds__(KT)
 diff_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool, DiffCache cache, T* __restrict__ out,
-                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                            const int* __restrict__ items, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                             const int* __restrict__ slots, const int* __restrict__ block_table, int nh, int dim,
                             float scale, float cap, int block, int window, float lambda, float eps, float out_scale,
                             int* __restrict__ status) {
@@ -181,7 +158,8 @@ diff_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool,
     float* sp1 = smem + 2 * dim;      // [KT] weights of the tile, map 1
     float* sp2 = sp1 + KT;            // [KT] map 2
     __shared__ float scratch[32];
-    const int t = blockIdx.x, h = blockIdx.y;
+    const int t = items ? items[blockIdx.x] : blockIdx.x, h = blockIdx.y;
+    if (t < 0) return;                                  // padding of the item list
     const int pos = positions[t];
     if (pos < 0) return;
     const int nkv = cache.nkv, vd = cache.vd, kd = cache.kd, ps = cache.page_size;
@@ -256,7 +234,8 @@ diff_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool,
 }
 
 ST_EXPORT int st_diff_attention_plain(const void* q, const void* pool, long long page_stride, long long entry_offset,
-                                      void* out, const int* positions, const int* seq_of_token, const int* slots,
+                                      void* out, const int* items, const int* positions, const int* seq_of_token,
+                                      const int* slots,
                                       const int* block_table, int max_pages, int n_tokens, int nh, int nkv, int dim,
                                       int vd, int page_size, float scale, float cap, int block, int window,
                                       float lambda, float eps, float out_scale, int* status, int dtype, void* stream) {
@@ -268,10 +247,10 @@ ST_EXPORT int st_diff_attention_plain(const void* q, const void* pool, long long
     dim3 grid(n_tokens, nh);
     const size_t smem = (size_t)(2 * dim + 2 * KT) * sizeof(float);
     if (dtype == 0)
-        diff_attention_plain_kernel<float><<<grid, KT, smem, s>>>((const float*)q, (const float*)pool, c, (float*)out, positions,
+        diff_attention_plain_kernel<float><<<grid, KT, smem, s>>>((const float*)q, (const float*)pool, c, (float*)out, items, positions,
             seq_of_token, slots, block_table, nh, dim, scale, cap, block, window, lambda, eps, out_scale, status);
     else if (dtype == 1)
-        diff_attention_plain_kernel<bf16><<<grid, KT, smem, s>>>((const bf16*)q, (const bf16*)pool, c, (bf16*)out, positions,
+        diff_attention_plain_kernel<bf16><<<grid, KT, smem, s>>>((const bf16*)q, (const bf16*)pool, c, (bf16*)out, items, positions,
             seq_of_token, slots, block_table, nh, dim, scale, cap, block, window, lambda, eps, out_scale, status);
     else return ST_ERR_BAD_DTYPE;
     return st_launch_status();

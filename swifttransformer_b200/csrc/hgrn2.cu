@@ -81,24 +81,158 @@ hgrn2_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
     for (int e = tid; e < dim * vd; e += nt) st[e] = S[e];
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same recurrence with the state in registers and the work of a head spread over blocks: a block owns
+// HC_COLS columns of S for one (request, head); eight lanes share a column, each with R consecutive rows of
+// it in registers (dim <= 8 R), and meet by shuffles for o = S^T q.  A warp owns four columns.  The blocks of
+// a head cannot normalise its output (each sees a slice of it): they leave o in float and
+// `hgrn2_norm_kernel` follows.  Per token the order of the sums is fixed, whatever the portion or the batch.
+#define HC_COLS 16
+#define HC_LANES 8
+
+template <int R> struct HcLayout {
+    static constexpr int LS = R >= 4 ? R + 4 : R + 1;       // floats between the rows of consecutive lanes (bank spread)
+    static constexpr int ROW = HC_LANES * LS;               // floats per token
+};
+
+template <typename T, int R>
+__global__ void __launch_bounds__(128)
+hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int v_off, const float* __restrict__ f_bias,
+                  const float* __restrict__ lower, float* __restrict__ state, float* __restrict__ o_raw,
+                  const int* __restrict__ positions, const int* __restrict__ q_start, const int* __restrict__ slots,
+                  int nh, int dim, int vd) {
+    using L = HcLayout<R>;
+    __shared__ __align__(16) float sq[HG_GROUP * L::ROW];
+    __shared__ __align__(16) float sf[HG_GROUP * L::ROW];
+    __shared__ float sv[HG_GROUP * HC_COLS];
+    const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * HC_COLS;
+    const int first = q_start[b], n = q_start[b + 1] - first;
+    if (n <= 0 || positions[first] < 0) return;           // padding of a fixed-shape step
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int l = lane >> 2, col = c0 + warp * 4 + (lane & 3);
+    float* st = state + ((size_t)slots[b] * nh + h) * dim * vd;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = l * R + r;
+        S[r] = (i < dim && col < vd) ? st[(size_t)i * vd + col] : 0.f;
+    }
+    for (int r0 = 0; r0 < n; r0 += HG_GROUP) {
+        const int rn = min(HG_GROUP, n - r0);
+        __syncthreads();
+        for (int e = tid; e < rn * HC_LANES * R; e += 128) {
+            const int k = e / (HC_LANES * R), i = e % (HC_LANES * R);
+            float qv = 0.f, fv = 1.f;                         // rows past dim: nothing written, nothing read
+            if (i < dim) {
+                const T* row = proj + (size_t)(first + r0 + k) * ld;
+                const float zq = to_f32(row[q_off + h * dim + i]);
+                const float zf = to_f32(row[f_off + h * dim + i]) + f_bias[h * dim + i];
+                const float lo = lower[h * dim + i];
+                qv = zq / (1.f + expf(-zq));
+                fv = lo + (1.f - lo) * (1.f / (1.f + expf(-zf)));
+            }
+            const int at = k * L::ROW + (i / R) * L::LS + i % R;
+            sq[at] = qv;
+            sf[at] = fv;
+        }
+        for (int e = tid; e < rn * HC_COLS; e += 128) {
+            const int k = e / HC_COLS, j = c0 + e % HC_COLS;
+            sv[e] = j < vd ? to_f32(proj[(size_t)(first + r0 + k) * ld + v_off + h * vd + j]) : 0.f;
+        }
+        __syncthreads();
+        for (int k = 0; k < rn; ++k) {
+            const float v = sv[k * HC_COLS + warp * 4 + (lane & 3)];
+            const float* fp = sf + k * L::ROW + l * L::LS;
+            const float* qp = sq + k * L::ROW + l * L::LS;
+            float f[R], qq[R];
+            if (R % 4 == 0) {
+#pragma unroll
+                for (int r = 0; r < R; r += 4) {
+                    *reinterpret_cast<float4*>(f + r) = *reinterpret_cast<const float4*>(fp + r);
+                    *reinterpret_cast<float4*>(qq + r) = *reinterpret_cast<const float4*>(qp + r);
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) { f[r] = fp[r]; qq[r] = qp[r]; }
+            }
+            float o = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                S[r] = fmaf(f[r], S[r], (1.f - f[r]) * v);
+                o = fmaf(S[r], qq[r], o);
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            o += __shfl_xor_sync(0xffffffffu, o, 8);
+            o += __shfl_xor_sync(0xffffffffu, o, 16);
+            if (l == 0 && col < vd) o_raw[((size_t)(first + r0 + k) * nh + h) * vd + col] = o;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = l * R + r;
+        if (i < dim && col < vd) st[(size_t)i * vd + col] = S[r];
+    }
+}
+
+// out[t][h] = o_raw[t][h] / sqrt(mean(o_raw[t][h]^2) + eps) * norm_w, a warp per (token, head)
+template <typename T>
+__global__ void __launch_bounds__(256)
+hgrn2_norm_kernel(const float* __restrict__ o_raw, const float* __restrict__ norm_w, float eps, T* __restrict__ out,
+                  const int* __restrict__ positions, int n_tokens, int nh, int vd) {
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= n_tokens * nh || positions[unit / nh] < 0) return;
+    const float* row = o_raw + (size_t)unit * vd;
+    float ss = 0.f;
+    for (int j = lane; j < vd; j += 32) ss = fmaf(row[j], row[j], ss);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)vd + eps);
+    for (int j = lane; j < vd; j += 32) out[(size_t)unit * vd + j] = from_f32<T>(row[j] * inv * norm_w[j]);
+}
+
 static size_t hgrn2_smem(int dim, int vd) {
     return ((size_t)dim * vd + 2 * HG_GROUP * dim + 2 * HG_GROUP * vd) * sizeof(float);
 }
 
 // proj: [tokens, ld] with the query, gate and value projections at column offsets q_off, f_off, v_off
 // state: [slots, nh, dim, vd] float; out: [tokens, nh * vd]
+// o_raw: float scratch [tokens, nh * vd] for the form with the state in registers (dim <= 128), or null for the
+// form with one block per head and the state in shared memory
 ST_EXPORT int st_hgrn2_scan(const void* proj, int ld, int q_off, int f_off, int v_off, const float* f_bias,
-                            const float* lower, const float* norm_w, float eps, float* state, void* out,
-                            const int* positions, const int* q_start, const int* slots, int n_seqs, int nh, int dim,
-                            int vd, int dtype, void* stream) {
-    if (n_seqs <= 0) return 0;
+                            const float* lower, const float* norm_w, float eps, float* state, void* out, float* o_raw,
+                            const int* positions, const int* q_start, const int* slots, int n_tokens, int n_seqs, int nh,
+                            int dim, int vd, int dtype, void* stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (nh <= 0 || dim <= 0 || vd <= 0) return ST_ERR_BAD_ARG;
+    if (dtype != 0 && dtype != 1) return ST_ERR_BAD_DTYPE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (o_raw && dim <= 128) {
+        dim3 grid(n_seqs, nh, (vd + HC_COLS - 1) / HC_COLS);
+#define HC_LAUNCH(T, R) hgrn2_cols_kernel<T, R><<<grid, 128, 0, s>>>((const T*)proj, ld, q_off, f_off, v_off, f_bias, lower,                                                                     state, o_raw, positions, q_start, slots, nh, dim, vd)
+#define HC_PICK(T)                                    \
+    do {                                              \
+        if (dim <= 8) HC_LAUNCH(T, 1);                \
+        else if (dim <= 16) HC_LAUNCH(T, 2);          \
+        else if (dim <= 32) HC_LAUNCH(T, 4);          \
+        else if (dim <= 64) HC_LAUNCH(T, 8);          \
+        else HC_LAUNCH(T, 16);                        \
+    } while (0)
+        if (dtype == 0) HC_PICK(float); else HC_PICK(bf16);
+#undef HC_PICK
+#undef HC_LAUNCH
+        int rc = st_launch_status();
+        if (rc) return rc;
+        const int units = n_tokens * nh;
+        if (dtype == 0)
+            hgrn2_norm_kernel<float><<<(units + 7) / 8, 256, 0, s>>>(o_raw, norm_w, eps, (float*)out, positions, n_tokens, nh, vd);
+        else
+            hgrn2_norm_kernel<bf16><<<(units + 7) / 8, 256, 0, s>>>(o_raw, norm_w, eps, (bf16*)out, positions, n_tokens, nh, vd);
+        return st_launch_status();
+    }
     const size_t smem = hgrn2_smem(dim, vd);
     if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;
     int threads = (vd + 31) / 32 * 32;
     if (threads < 128) threads = 128;
     if (threads > 1024) threads = 1024;
-    cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_seqs, nh);
 #define HG_LAUNCH(T)                                                                                                  \
     do {                                                                                                              \
@@ -108,11 +242,11 @@ ST_EXPORT int st_hgrn2_scan(const void* proj, int ld, int q_off, int f_off, int 
             if (e != cudaSuccess) return (int)e;                                                                      \
         }                                                                                                             \
         hgrn2_scan_kernel<T><<<grid, threads, smem, s>>>((const T*)proj, ld, q_off, f_off, v_off, f_bias, lower,      \
-                                                         norm_w, eps, state, (T*)out, positions, q_start, slots, nh, dim, vd); \
+                                                         norm_w, eps, state, (T*)out, positions, q_start, slots, nh,  \
+                                                         dim, vd);                                                    \
     } while (0)
     if (dtype == 0) HG_LAUNCH(float);
-    else if (dtype == 1) HG_LAUNCH(bf16);
-    else return ST_ERR_BAD_DTYPE;
+    else HG_LAUNCH(bf16);
 #undef HG_LAUNCH
     return st_launch_status();
 }

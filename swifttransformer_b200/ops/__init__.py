@@ -765,31 +765,62 @@ def diff_attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: t
                          seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
                          nkv: int, dim: int, vd: int, page_size: int, scale: float, cap: float, block: int,
                          window: int, lam: float, eps: float, out_scale: float,
-                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         status: Optional[torch.Tensor] = None, items: Optional[torch.Tensor] = None,
+                         n_items: int = 0) -> torch.Tensor:
     """Differential attention of the step's queries q [tokens, nh * 2 * dim] over the paged cache, one block per
     (token, head), float arithmetic for either type: out [tokens, nh * vd] =
-    rms(softmax(cap(q1 k1)) V - lam * softmax(cap(q2 k2)) V) * out_scale."""
+    rms(softmax(cap(q1 k1)) V - lam * softmax(cap(q2 k2)) V) * out_scale.  ``items``: the token indices to serve
+    (-1: none), ``n_items`` of them; None: every token."""
     stride, offset = _flat_pool(pool, layer, nkv, dim, vd, page_size)
-    _check(lib().st_diff_attention_plain(_p(q), _p(pool), stride, offset, _p(out), _p(positions), _p(seq_of_token),
-                                         _p(slots), _p(block_table), block_table.shape[1], q.shape[0], nh, nkv, dim,
+    _check(lib().st_diff_attention_plain(_p(q), _p(pool), stride, offset, _p(out), _p(items), _p(positions), _p(seq_of_token),
+                                         _p(slots), _p(block_table), block_table.shape[1],
+                                         n_items if items is not None else q.shape[0], nh, nkv, dim,
                                          vd, page_size, _f(scale), _f(cap), block, window, _f(lam), _f(eps),
                                          _f(out_scale), _p(status), _dt(q), _stream()), "diff_attention_plain")
+    return out
+
+
+def diff_attention_tiles_applies(q: torch.Tensor, dim: int, vd: int) -> bool:
+    """Whether the tensor-core kernel for prompt portions takes these sizes: bfloat16, dim and vd multiples of 8,
+    dim <= 128, vd <= 256."""
+    return q.is_cuda and q.dtype == torch.bfloat16 and bool(lib().st_diff_attention_tiles_applies(dim, vd))
+
+
+def diff_attention_tiles(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, tiles: torch.Tensor,
+                         n_tiles: int, tile_rows: int, q_start: torch.Tensor, start_pos: torch.Tensor,
+                         slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, dim: int, vd: int,
+                         page_size: int, scale: float, cap: float, block: int, window: int, lam: float, eps: float,
+                         out_scale: float, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same attention for tiles of ``tile_rows`` query rows (tiles: int32 [n_tiles, 2] = request of the step,
+    offset of the tile among its new tokens) on the warp-level tensor cores, bfloat16 only."""
+    if not diff_attention_tiles_applies(q, dim, vd):
+        raise KernelError("diff_attention_tiles: bfloat16, dim and vd multiples of 8, dim <= 128, vd <= 256")
+    stride, offset = _flat_pool(pool, layer, nkv, dim, vd, page_size)
+    _check(lib().st_diff_attention_tiles(_p(q), _p(pool), stride, offset, _p(out), _p(tiles), n_tiles, tile_rows,
+                                         _p(q_start), _p(start_pos), _p(slots), _p(block_table), block_table.shape[1],
+                                         nh, nkv, dim, vd, page_size, _f(scale), _f(cap), block, window, _f(lam),
+                                         _f(eps), _f(out_scale), _p(status), _stream()), "diff_attention_tiles")
     return out
 
 
 # ------------------------------------------------------------ gated linear recurrence
 def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor, lower: torch.Tensor,
                norm_w: torch.Tensor, eps: float, state: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
-               q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, nh: int, dim: int, vd: int) -> torch.Tensor:
+               q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, nh: int, dim: int, vd: int,
+               scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The HGRN2 recurrence over each request's tokens of the step, from the fused projection (queries, gates and
     values at column offsets q_off, f_off, v_off): S <- diag(f) S + (1 - f) v^T, o = S^T silu(q), f = lower +
     (1 - lower) sigmoid(gate + f_bias); out [tokens, nh * vd] = rms(o) * norm_w per head.  ``state``: float32
-    [slots, nh, dim, vd], read and moved on."""
+    [slots, nh, dim, vd], read and moved on.  ``scratch``: float32, at least tokens * nh * vd elements: with it (and
+    dim <= 128) the state is carried in registers and a head's columns are spread over blocks; without it one block
+    per (request, head) keeps the state in shared memory."""
     assert proj.is_contiguous() and out.is_contiguous() and out.shape == (proj.shape[0], nh * vd)
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (nh, dim, vd)
+    if scratch is not None:
+        assert scratch.dtype == torch.float32 and scratch.numel() >= out.numel()
     _check(lib().st_hgrn2_scan(_p(proj), proj.shape[1], q_off, f_off, v_off, _p(f_bias), _p(lower), _p(norm_w),
-                               _f(eps), _p(state), _p(out), _p(positions), _p(q_start), _p(slots), n_seqs, nh, dim, vd, _dt(proj),
-                               _stream()), "hgrn2_scan")
+                               _f(eps), _p(state), _p(out), _p(scratch), _p(positions), _p(q_start), _p(slots),
+                               proj.shape[0], n_seqs, nh, dim, vd, _dt(proj), _stream()), "hgrn2_scan")
     return out
 
 

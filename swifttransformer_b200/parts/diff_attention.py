@@ -25,7 +25,8 @@ import torch
 
 from .. import ops
 from ..weights.spec import MATRIX, VECTOR, GAIN, ParamSpec
-from .base import MIXERS, Delta, Mixer, PagedKVSpec, StateSpec
+from .attention import PagedAttentionPlan
+from .base import MIXERS, Delta, Mixer, PagedKVSpec, StateSpec, StepPlan
 
 
 @MIXERS.register("differential_attention")
@@ -46,6 +47,13 @@ class DifferentialAttention(Mixer):
         self.qw, self.kw, self.vw = num_heads * 2 * dim, num_kv_heads * 2 * dim, num_kv_heads * vdim
         self.w_qkv = self.w_o = self.conv_w = self.q_norm = self.k_norm = None
         self.lam = 0.0
+        self._plan: Optional[PagedAttentionPlan] = None
+
+    def step_plan(self) -> StepPlan:
+        # the paged attention's sorting of a step's tokens: portions in tiles, short ones and single tokens as items
+        if self._plan is None:
+            self._plan = PagedAttentionPlan()
+        return self._plan
 
     def param_specs(self) -> List[ParamSpec]:
         n, specs = self.names, []
@@ -87,10 +95,22 @@ class DifferentialAttention(Mixer):
             ops.conv_state_update(proj, self.qw + self.kw + self.vw, tails.state, ctx.positions, ctx.q_start, ctx.slots,
                                   ctx.n_seqs)
         o = torch.empty((n, self.nh * self.vdim), dtype=h.dtype, device=h.device)
-        ops.diff_attention_plain(q, kv.pool, kv.layer, o, ctx.positions, ctx.seq_of_token, ctx.slots, kv.block_table,
-                                 self.nh, self.nkv, self.dim, self.vdim, kv.page_size, self.scale, self.softcap,
-                                 self.block or 0, self.window or 0, self.lam, self.eps, 1.0 - self.diff,
-                                 status=ctx.status)
+        consts = (self.nh, self.nkv, self.dim, self.vdim, kv.page_size, self.scale, self.softcap, self.block or 0,
+                  self.window or 0, self.lam, self.eps, 1.0 - self.diff)
+        if ops.diff_attention_tiles_applies(q, self.dim, self.vdim):
+            # prompt portions in tiles of query rows on the tensor cores, short portions and single tokens one by one
+            plan = ctx.plan(PagedAttentionPlan.name)
+            if plan.n_tiles:
+                ops.diff_attention_tiles(q, kv.pool, kv.layer, o, plan.tiles, plan.n_tiles, self._plan.tile_rows,
+                                         ctx.q_start, ctx.start_pos, ctx.slots, kv.block_table, *consts,
+                                         status=ctx.status)
+            if plan.n_items:
+                ops.diff_attention_plain(q, kv.pool, kv.layer, o, ctx.positions, ctx.seq_of_token, ctx.slots,
+                                         kv.block_table, *consts, status=ctx.status, items=plan.items,
+                                         n_items=plan.n_items)
+        else:
+            ops.diff_attention_plain(q, kv.pool, kv.layer, o, ctx.positions, ctx.seq_of_token, ctx.slots,
+                                     kv.block_table, *consts, status=ctx.status)
         return Delta(ops.linear(o, self.w_o))
 
     def param_bytes(self) -> int:

@@ -128,9 +128,10 @@ def test_norm_add_and_gated_act(dtype, width):
 
 
 # ------------------------------------------------------------------------------------------ the recurrence
+@pytest.mark.parametrize("in_registers", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,d,dv", [(2, 20, 40), (1, 64, 16), (3, 8, 130)])
-def test_hgrn2_scan_in_portions_and_token_by_token(dtype, H, d, dv):
+@pytest.mark.parametrize("H,d,dv", [(2, 20, 40), (1, 64, 16), (3, 8, 130), (2, 128, 36), (1, 5, 7)])
+def test_hgrn2_scan_in_portions_and_token_by_token(dtype, H, d, dv, in_registers):
     from swifttransformer_b200 import ops
     rng = np.random.default_rng(H * 100 + d)
     T = 75
@@ -150,7 +151,8 @@ def test_hgrn2_scan_in_portions_and_token_by_token(dtype, H, d, dv):
             rows = dev(np.concatenate([proj[start:start + n], np.full((2, proj.shape[1]), 50.0)]), TD[dtype])
             out = torch.zeros((st.n_rows, H * dv), dtype=TD[dtype], device="cuda")
             ops.hgrn2_scan(rows, 0, H * d, 2 * H * d, dev(f_bias), dev(lower), dev(norm_w), 1e-5, state, out,
-                           st.positions, st.q_start, st.slots, st.n_seqs, H, d, dv)
+                           st.positions, st.q_start, st.slots, st.n_seqs, H, d, dv,
+                           scratch=torch.full((st.n_rows * H * dv,), 9.0, device="cuda") if in_registers else None)
             got[start:start + n] = out.float().cpu().numpy()[:n]
         assert torch.all(state[0] == 3.0) and torch.all(state[2] == 0.0)
         assert np.abs(got - ref).max() < (2e-5 if dtype == "float32" else 3e-2) * np.abs(ref).max(), sizes
@@ -165,8 +167,9 @@ def test_hgrn2_padding_request_of_a_decode_step_leaves_slot_zero_alone():
     st.q_start, st.slots, st.n_seqs = ints([0, 1, 2]), ints([0, 0]), 2
     rows = torch.ones((2, 2 * H * d + H * dv), device="cuda")
     out = torch.zeros((2, H * dv), device="cuda")
-    ops.hgrn2_scan(rows, 0, H * d, 2 * H * d, dev(np.zeros(H * d)), dev(np.zeros(H * d)), dev(np.ones(dv)), 1e-5,
-                   state, out, st.positions, st.q_start, st.slots, st.n_seqs, H, d, dv)
+    for scratch in (None, torch.zeros(2 * H * dv, device="cuda")):
+        ops.hgrn2_scan(rows, 0, H * d, 2 * H * d, dev(np.zeros(H * d)), dev(np.zeros(H * d)), dev(np.ones(dv)), 1e-5,
+                       state, out, st.positions, st.q_start, st.slots, st.n_seqs, H, d, dv, scratch=scratch)
     conv = torch.full((2, 2, 16), 5.0, device="cuda")
     ops.conv_state_update(rows[:, :16].contiguous(), 16, conv, st.positions, st.q_start, st.slots, 2)
     assert torch.all(state == 5.0) and torch.all(conv == 5.0)
@@ -213,9 +216,28 @@ class PagedHarness:
                              p["rot_dims"], q, self.pool, self.entry, st.positions, st.seq, st.q_start, st.slots,
                              self.table, self.H, self.G, self.d, self.dv, self.ps, self.status)
         ops.conv_state_update(proj, self.C, self.state, st.positions, st.q_start, st.slots, st.n_seqs)
-        ops.diff_attention_plain(q, self.pool, self.entry, out, st.positions, st.seq, st.slots, self.table, self.H,
-                                 self.G, self.d, self.dv, self.ps, p["scale"], p["cap"], p["block"], 0, p["lam"],
-                                 p["eps"], p["out_scale"], status=self.status)
+        consts = (self.H, self.G, self.d, self.dv, self.ps, p["scale"], p["cap"], p["block"], 0, p["lam"], p["eps"],
+                  p["out_scale"])
+        if kernel == "tiles" and ops.diff_attention_tiles_applies(q, self.d, self.dv):
+            # as the mixer does it: portions of 16 tokens and more in tiles of 128 rows, the rest one by one
+            tiles, items, first = [], [], 0
+            for i, (slot, start, n) in enumerate(entries):
+                if n >= 16:
+                    tiles += [(i, off) for off in range(0, n, 128)]
+                else:
+                    items += list(range(first, first + n))
+                first += n
+            tiles.append((0, 1 << 24))                   # a padding tile
+            items += [-1, -1]
+            if len(tiles) > 1:
+                ops.diff_attention_tiles(q, self.pool, self.entry, out, ints(tiles), len(tiles), 128, st.q_start,
+                                         ints([e[1] for e in entries] + [0]), st.slots, self.table, *consts,
+                                         status=self.status)
+            ops.diff_attention_plain(q, self.pool, self.entry, out, st.positions, st.seq, st.slots, self.table, *consts,
+                                     status=self.status, items=ints(items), n_items=len(items))
+        else:
+            ops.diff_attention_plain(q, self.pool, self.entry, out, st.positions, st.seq, st.slots, self.table, *consts,
+                                     status=self.status)
         assert int(self.status.item()) == 0
         return out.float().cpu().numpy()[:st.n]
 
@@ -251,14 +273,19 @@ def plain_attention(c, rows, H, G, d, dv):
 SHAPES = [  # H, G, d, dv, taps, rot_dims, block, cap, page
     (4, 2, 16, 24, 3, 8, 40, 30.0, 16),
     (2, 2, 32, 16, 2, 32, 16, 0.0, 8),
-    (3, 1, 10, 70, 4, 0, None, 5.0, 4),
+    (3, 1, 10, 70, 4, 0, None, 5.0, 4),          # sizes the tile kernel does not take
     (1, 1, 64, 128, 1, 64, 100, 50.0, 32),
+    (2, 1, 40, 72, 2, 16, 90, 20.0, 16),         # sizes between the tile kernel's rounded ones
+    (1, 1, 128, 256, 2, 128, None, 0.0, 64),
 ]
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+KERNELS = [("float32", "plain"), ("bfloat16", "plain"), ("bfloat16", "tiles")]
+
+
+@pytest.mark.parametrize("dtype,kernel", KERNELS)
 @pytest.mark.parametrize("shape", SHAPES)
-def test_differential_attention_whole_portions_and_decoding(dtype, shape):
+def test_differential_attention_whole_portions_and_decoding(dtype, kernel, shape):
     H, G, d, dv, taps, rot_dims, block, cap, page = shape
     T = 150
     c, rows = attention_case(H, G, d, dv, taps, rot_dims, block, cap, seed=H * 7 + d, T=T)
@@ -269,14 +296,14 @@ def test_differential_attention_whole_portions_and_decoding(dtype, shape):
     for slot, sizes in ((0, (T,)), (2, (100, 1, 1, 1, 1, 1, 1)), (0, (3, 2, 37, 1, 2, 50, 2, 2))):
         got = np.zeros_like(ref)
         for start, n in portions(T, sizes):
-            got[start:start + n] = hz.run([(slot, start, n)], rows[start:start + n], p)
+            got[start:start + n] = hz.run([(slot, start, n)], rows[start:start + n], p, kernel)
         err = np.abs(got - ref).max(axis=1)
         assert err.max() < tol, (sizes, int(np.argmax(err > tol)), float(err.max()))
         hz.release(slot)          # the next case gets these pages and this slot again, with what they held
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_differential_attention_batch_of_unequal_requests_equals_each_alone(dtype):
+@pytest.mark.parametrize("dtype,kernel", KERNELS)
+def test_differential_attention_batch_of_unequal_requests_equals_each_alone(dtype, kernel):
     H, G, d, dv, taps, rot_dims, block, cap, page = SHAPES[0]
     cases = [attention_case(H, G, d, dv, taps, rot_dims, block, cap, seed=5, T=T) for T in (90, 33, 61)]
     c = cases[0][0]
@@ -293,7 +320,7 @@ def test_differential_attention_batch_of_unequal_requests_equals_each_alone(dtyp
             if n:
                 entries.append((r, at[r], n))
                 parts.append(cases[r][1][at[r]:at[r] + n])
-        out, k = hz.run(entries, np.concatenate(parts), p), 0
+        out, k = hz.run(entries, np.concatenate(parts), p, kernel), 0
         for r, start, n in entries:
             got[r][start:start + n] = out[k:k + n]
             k += n
@@ -304,8 +331,8 @@ def test_differential_attention_batch_of_unequal_requests_equals_each_alone(dtyp
 
 
 @pytest.mark.parametrize("decode", [False, True])
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_one_key_decides_at_block_edges_page_borders_and_far_back(dtype, decode):
+@pytest.mark.parametrize("dtype,kernel", KERNELS)
+def test_one_key_decides_at_block_edges_page_borders_and_far_back(dtype, kernel, decode):
     """The query at position t and the key at position j are scaled so that, if j is visible, map 1 puts all
     its weight on j: the result is then v_j (normalised).  j just inside the query's block, just outside it,
     on either side of a page border, the first key of the sequence, and hundreds of keys back."""
@@ -330,10 +357,10 @@ def test_one_key_decides_at_block_edges_page_borders_and_far_back(dtype, decode)
             p = on_device(c, None)
             hz = PagedHarness(H, G, d, dv, taps, page, dtype, seed=t)
             if decode:
-                hz.run([(1, 0, t)], rows[:t], p)
-                got = hz.run([(1, t, 1)], rows[t:t + 1], p)[0]
+                hz.run([(1, 0, t)], rows[:t], p, kernel)
+                got = hz.run([(1, t, 1)], rows[t:t + 1], p, kernel)[0]
             else:
-                got = hz.run([(1, 0, t + 1)], rows[:t + 1], p)[t]
+                got = hz.run([(1, 0, t + 1)], rows[:t + 1], p, kernel)[t]
             assert np.abs(got - ref[t]).max() < (1e-4 if dtype == "float32" else 4e-2), (block, t, j)
 
 
