@@ -12,7 +12,9 @@ single-GPU and exits with 2.
 
 ``--only decode|prefill`` run one small measurement (for profiling); ``--only mixed`` runs a continuous
 batch of requests of random lengths (prompt portions of 512 tokens beside decoded tokens) through
-``LLMEngine.generate`` and reports tokens per second, steps and preemptions.
+``LLMEngine.generate`` and reports tokens per second, steps and preemptions.  ``--only designs`` measures a
+Fanidra model beside an OPT model of equal width, depth and parameter count (prefill, decode, and the device time
+of every operation of one step of each kind; ``--model-name w2048|w4096`` picks one size, ``--layers`` the depth).
 """
 import argparse
 import json
@@ -95,6 +97,140 @@ def prefill_flops(cfg, n_layers, n):
     return n_layers * (per_layer + attn) + 2 * H * V   # + the output product for the one wanted row
 
 
+# Layer sizes for ``--only designs``: a Fanidra model beside an OPT model of the same width, depth and (nearly) the
+# same number of parameters per layer (a gated feed-forward has three matrices: its inner size is two thirds of
+# OPT's).  Every fourth layer of the Fanidra model is the recurrence, the others attention.
+DESIGN_SIZES = {
+    "w2048": dict(width=2048, opt_heads=32, opt_ffn=8192, heads=16, kv_heads=4, dim=64, vdim=128, ff=5504,
+                  rec_heads=16, rec_dim=128, rec_vdim=128, block=512),
+    "w4096": dict(width=4096, opt_heads=32, opt_ffn=16384, heads=32, kv_heads=8, dim=64, vdim=128, ff=10944,
+                  rec_heads=32, rec_dim=128, rec_vdim=128, block=512),
+}
+
+
+def compare_designs(args, peaks):
+    """Prefill (2048 tokens) and decode (batch 8 behind 512-token prompts) of a Fanidra model and of an OPT model
+    of equal size, random weights, device-timed; and the device time of every operation of one prefill step and one
+    decode step launched kernel by kernel.  One JSON line per (size, design)."""
+    import gc
+    import numpy as np
+    import torch
+    from swifttransformer_b200 import ops
+    from swifttransformer_b200.config import FanidraConfig, OptConfig
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.engine.step import StepEntry
+    from swifttransformer_b200.models import random_model
+    from swifttransformer_b200.ops import timing
+
+    torch.cuda.set_device(0)
+    rng = np.random.default_rng(0)
+    n_layers, vocab, P, batch, n_prefill = args.layers or 4, 32000, 512, args.batch, 2048
+    K, W = min(args.steps, 64), args.warmup
+
+    def configs(z):
+        att = {"type": "attention", "mlp": {"kind": "dense", "ff": z["ff"]},
+               "mixer": dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], conv=4,
+                             scale=z["dim"] ** -0.5, diff=0.3, softcap=50.0, mask={"size": z["block"]},
+                             rot={"dims": z["dim"], "base": 1e6})}
+        rec = {"type": "hgrn2", "mlp": {"kind": "dense", "ff": z["ff"]},
+               "mixer": dict(heads=z["rec_heads"], dim=z["rec_dim"], vdim=z["rec_vdim"])}
+        fan = FanidraConfig.from_dict(dict(architecture="Fanidra", vocab=vocab, width=z["width"], norm={"eps": 1e-5},
+                                           residual_mult=0.3, embedding={"scale": 12.0}, canon={"taps": 3},
+                                           layers=[rec if i % 4 == 1 else att for i in range(n_layers)]))
+        opt = OptConfig.from_dict(dict(vocab_size=vocab, hidden_size=z["width"], num_hidden_layers=n_layers,
+                                       ffn_dim=z["opt_ffn"], num_attention_heads=z["opt_heads"],
+                                       max_position_embeddings=4096))
+        return {"fanidra": fan, "opt": opt}
+
+    def engine(model, graphs=True):
+        gc.collect()
+        torch.cuda.empty_cache()
+        pages = batch * ((P + 2 * (K + W) + 32) // 16 + 2) + n_prefill // 16 + 8
+        return LLMEngine(model, page_size=16, num_pages=pages, max_batch_tokens=max(n_prefill, batch * P),
+                         chunk_size=n_prefill, max_num_seqs=batch, max_seq_len=4096, use_cuda_graphs=graphs)
+
+    def run(model, graphs, steps, warmup):
+        """(prefill ms, decode ms per step) on the device."""
+        eng = engine(model, graphs)
+        times = []
+        for _ in range(4 if graphs else 2):
+            slot = eng.cache.alloc_slot()
+            toks = rng.integers(3, vocab, n_prefill).tolist()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.runner.step([StepEntry(slot, toks, 0, [n_prefill - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            eng.cache.free_slot(slot)
+        slots = [eng.cache.alloc_slot() for _ in range(batch)]
+        for s in slots:
+            eng.runner.step([StepEntry(s, rng.integers(3, vocab, P).tolist(), 0, [])])
+        lens = [P] * batch
+
+        def one():
+            logits = eng.runner.step([StepEntry(slots[i], [int(rng.integers(3, vocab))], lens[i], [0]) for i in range(batch)])
+            ops.argmax(logits)
+            for i in range(batch):
+                lens[i] += 1
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        eng.runner.check_status()
+        return min(times[1:]), e0.elapsed_time(e1) / steps, eng
+
+    def per_operation(model):
+        """Device time per operation of one prefill step and one decode step launched kernel by kernel."""
+        eng = engine(model, graphs=False)
+        out = {}
+        slot = eng.cache.alloc_slot()
+        toks = rng.integers(3, vocab, n_prefill).tolist()
+        eng.runner.step([StepEntry(slot, toks, 0, [n_prefill - 1])])
+        eng.cache.free_slot(slot)
+        slot = eng.cache.alloc_slot()
+        timing.start()
+        eng.runner.step([StepEntry(slot, toks, 0, [n_prefill - 1])])
+        out["prefill"] = {k: [v["calls"], round(v["ms"], 4)] for k, v in timing.stop().items()}
+        eng.cache.free_slot(slot)
+        slots = [eng.cache.alloc_slot() for _ in range(batch)]
+        for s in slots:
+            eng.runner.step([StepEntry(s, rng.integers(3, vocab, P).tolist(), 0, [])])
+        step = lambda k: eng.runner.step([StepEntry(slots[i], [5 + k], P + k, [0]) for i in range(batch)])
+        step(0)
+        timing.start()
+        step(1)
+        out["decode"] = {k: [v["calls"], round(v["ms"], 4)] for k, v in timing.stop().items()}
+        return out
+
+    for name in (args.model_name,) if args.model_name in DESIGN_SIZES else tuple(DESIGN_SIZES):
+        for design, cfg in configs(DESIGN_SIZES[name]).items():
+            model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            with ClockSampler(0) as clocks:
+                pre_ms, dec_ms, eng = run(model, True, K, W)
+            step_bytes = model.step_param_bytes() + batch * (P + W + K / 2) * eng.cache.bytes_per_token()
+            line = {"only": "designs", "size": name, "design": design, "layers": n_layers, "width": cfg.to_dict().get("width", 0) or cfg.hidden_size,
+                    "param_bytes_per_step": model.step_param_bytes(), "prefill_tokens": n_prefill,
+                    "prefill_ms": round(pre_ms, 4), "prefill_tok_s": round(n_prefill / pre_ms * 1e3, 1),
+                    "decode_batch": batch, "decode_ms_per_step": round(dec_ms, 4),
+                    "decode_tok_s": round(batch / dec_ms * 1e3, 1),
+                    "decode_hbm_frac": round(step_bytes / (dec_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                    "kernels_per_decode_step": eng.runner.kernels_last_step, "clocks": clocks.summary(),
+                    "peaks": peaks["source"]}
+            del eng
+            if not args.no_points:
+                line["operations"] = per_operation(model)
+            print(json.dumps(line), flush=True)
+            del model
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -111,7 +247,7 @@ def main():
                     help="with --only decode: same number of layers and kernels, but hidden size 64, so that the "
                          "step time is what the chain of dependent launches costs by itself")
     ap.add_argument("--rows", type=int, nargs="*", default=[16, 32, 64], help="with --only products: token counts")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "products"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "products", "designs"],
                     help="run just the device-timed decode loop or just the prefill (for profiling small cases), or "
                          "the mixed continuous batch: --requests requests with prompt lengths uniform in [16,1536] "
                          "and output lengths uniform in [16,512], prompt portions of 512 tokens beside decoded "
@@ -135,6 +271,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.only == "designs":
+        return compare_designs(args, load_peaks())
 
     import dataclasses
     import gc

@@ -66,6 +66,24 @@ class _Entry:
         return self._views[writable]
 
 
+def _leaves(key, spec):
+    """The single needs of a cache entry with their paths: [((entry, component, ...), spec)]."""
+    if isinstance(spec, (tuple, list)):
+        out = []
+        for j, sub in enumerate(spec):
+            out += _leaves(key + (j,), sub)
+        return out
+    return [(key, spec)]
+
+
+def _nested_maker(key, spec, makers):
+    """writable -> the views of a cache entry, nested as its needs are."""
+    if isinstance(spec, (tuple, list)):
+        subs = [_nested_maker(key + (j,), sub, makers) for j, sub in enumerate(spec)]
+        return lambda w: tuple(m(w) for m in subs)
+    return makers[key]
+
+
 class PagedGroup:
     def __init__(self, spec: PagedKVSpec, entries: List[int], page_size: int, num_pages: int, max_seqs: int,
                  max_pages_per_seq: int, dtype: torch.dtype, device: torch.device):
@@ -173,37 +191,26 @@ class CacheManager:
         # need is a leaf, known by its path (entry, component, ...), and the layer step gets views nested alike.
         makers: Dict[Any, Any] = {}
         by_spec: Dict[PagedKVSpec, List[Any]] = {}
-
-        def walk(key, spec):
-            if isinstance(spec, (tuple, list)):
-                for j, sub in enumerate(spec):
-                    walk(key + (j,), sub)
-            elif isinstance(spec, PagedKVSpec):
-                by_spec.setdefault(spec, []).append(key)
-            elif isinstance(spec, StateSpec):
-                t = torch.zeros((max_seqs,) + tuple(spec.shape), dtype=spec.dtype, device=self.device)
-                self.states[key[0] if len(key) == 1 else key] = t
-                makers[key] = lambda w, t=t: StateView(t, w)
-            elif spec is None:
-                makers[key] = lambda w: None
-            else:
-                raise TypeError(f"cache entry {key[0]}: unknown cache spec {spec!r}")
-
-        def maker(key, spec):
-            if isinstance(spec, (tuple, list)):
-                subs = [maker(key + (j,), sub) for j, sub in enumerate(spec)]
-                return lambda w, subs=subs: tuple(m(w) for m in subs)
-            return makers[key]
-
         for i, spec in enumerate(cache_specs):
-            walk((i,), spec)
+            for key, leaf in _leaves((i,), spec):
+                if isinstance(leaf, PagedKVSpec):
+                    by_spec.setdefault(leaf, []).append(key)
+                elif isinstance(leaf, StateSpec):
+                    t = torch.zeros((max_seqs,) + tuple(leaf.shape), dtype=leaf.dtype, device=self.device)
+                    self.states[key[0] if len(key) == 1 else key] = t
+                    makers[key] = lambda w, t=t: StateView(t, w)
+                elif leaf is None:
+                    makers[key] = lambda w: None
+                else:
+                    raise TypeError(f"cache entry {i}: unknown cache spec {leaf!r}")
         for spec, keys in by_spec.items():
-            g = PagedGroup(spec, [k[0] if len(k) == 1 else k for k in keys], page_size, num_pages, max_seqs, self.max_pages_per_seq, dtype, self.device)
+            g = PagedGroup(spec, [k[0] if len(k) == 1 else k for k in keys], page_size, num_pages, max_seqs,
+                           self.max_pages_per_seq, dtype, self.device)
             self.groups.append(g)
             for k, key in enumerate(keys):
                 makers[key] = lambda w, g=g, k=k: PagedCacheView(g.kv, k, g.block_table, page_size, w, g.spec)
         for i, spec in enumerate(cache_specs):
-            self._entries[i] = _Entry(maker((i,), spec))
+            self._entries[i] = _Entry(_nested_maker((i,), spec, makers))
         self._free_slots = list(range(max_seqs - 1, -1, -1))
         self._live = [False] * max_seqs
         self.lengths = [0] * max_seqs
