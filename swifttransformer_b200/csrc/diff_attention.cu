@@ -30,16 +30,18 @@
 //
 // proj:  [n_tokens, ld] the fused projection q | k | v as the product left it (before the convolution)
 // conv_w: [channels, taps] float, channels = nh*2*dim + nkv*2*dim + nkv*vd in the projection's order
-// state: [slots, taps-1, channels] float, read only (conv_state_update moves it afterwards)
+// state: [slots, taps-1, channels] float: read only (conv_state_update moves it afterwards), or, with move_state
+// (steps in which every request brings exactly one token), moved on here
 template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS)
 diff_qkv_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ conv_w,
-                        const float* __restrict__ state, int taps, const float* __restrict__ q_norm,
+                        float* __restrict__ state, int move_state, int taps, const float* __restrict__ q_norm,
                         const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int rot_dims,
                         T* __restrict__ q_out, T* __restrict__ pool, DiffCache cache,
                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                         const int* __restrict__ q_start, const int* __restrict__ slots,
                         const int* __restrict__ block_table, int nh, int dim, int write_kv, int* __restrict__ status) {
+    ST_PDL_TRIGGER();
     const int t = blockIdx.x;
     const int pos = positions[t];
     if (pos < 0) return;
@@ -54,7 +56,7 @@ diff_qkv_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restr
     const int page = block_table[(size_t)slot * cache.max_pages + pos / cache.page_size];
     const int pip = pos % cache.page_size;
     if (page < 0 && write_kv && status && threadIdx.x == 0) *status = 1;
-    const float* st = state + (size_t)slot * keep * channels;
+    float* st = state + (size_t)slot * keep * channels;
     for (int u = warp; u < units; u += nwarp) {
         const bool is_q = u < q_units, is_k = !is_q && u < q_units + k_units;
         const int width = (is_q || is_k) ? dim : vd;
@@ -71,14 +73,18 @@ diff_qkv_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restr
             for (int half = 0; half < 2; ++half) {
                 if (e + half >= width) continue;
                 const int c = ch0 + e + half;
-                float y = 0.f;
+                float y = 0.f, vv[CONV_MAX_TAPS];
                 for (int j = 0; j < taps; ++j) {
                     const int back = keep - j;            // the input `back` positions before this token
                     float v;
                     if (back <= i) v = to_f32(proj[(size_t)(t - back) * ld + c]);
                     else v = st[(size_t)(keep - (back - i)) * channels + c];   // zero before the request's start
+                    vv[j] = v;
                     y = fmaf(conv_w[(size_t)c * taps + j], v, y);
                 }
+                // every request brings one token: this thread alone reads and writes the channel's state
+                if (move_state)
+                    for (int j = 0; j < keep; ++j) st[(size_t)j * channels + c] = vv[j + 1];
                 if (half) x1[r] = y; else x0[r] = y;
                 ss += y * y;
             }
@@ -116,7 +122,7 @@ diff_qkv_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restr
     }
 }
 
-ST_EXPORT int st_diff_qkv_prepare(const void* proj, int ld, const float* conv_w, const float* state, int taps,
+ST_EXPORT int st_diff_qkv_prepare(const void* proj, int ld, const float* conv_w, float* state, int move_state, int taps,
                                   const float* q_norm, const float* k_norm, float eps, const float* inv_freq,
                                   int rot_dims, void* q_out, void* pool, long long page_stride, long long entry_offset,
                                   const int* positions, const int* seq_of_token, const int* q_start, const int* slots,
@@ -130,11 +136,11 @@ ST_EXPORT int st_diff_qkv_prepare(const void* proj, int ld, const float* conv_w,
     const DiffCache c = {max_pages, page_size, nkv, 2 * dim, vd, page_stride, entry_offset};
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == 0)
-        diff_qkv_prepare_kernel<float><<<n_tokens, PREP_THREADS, 0, s>>>((const float*)proj, ld, conv_w, state, taps, q_norm,
+        diff_qkv_prepare_kernel<float><<<n_tokens, PREP_THREADS, 0, s>>>((const float*)proj, ld, conv_w, state, move_state, taps, q_norm,
             k_norm, eps, inv_freq, rot_dims, (float*)q_out, (float*)pool, c, positions, seq_of_token, q_start, slots,
             block_table, nh, dim, write_kv, status);
     else if (dtype == 1)
-        diff_qkv_prepare_kernel<bf16><<<n_tokens, PREP_THREADS, 0, s>>>((const bf16*)proj, ld, conv_w, state, taps, q_norm,
+        diff_qkv_prepare_kernel<bf16><<<n_tokens, PREP_THREADS, 0, s>>>((const bf16*)proj, ld, conv_w, state, move_state, taps, q_norm,
             k_norm, eps, inv_freq, rot_dims, (bf16*)q_out, (bf16*)pool, c, positions, seq_of_token, q_start, slots,
             block_table, nh, dim, write_kv, status);
     else return ST_ERR_BAD_DTYPE;
@@ -158,6 +164,7 @@ diff_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool,
     float* sp1 = smem + 2 * dim;      // [KT] weights of the tile, map 1
     float* sp2 = sp1 + KT;            // [KT] map 2
     __shared__ float scratch[32];
+    ST_PDL_TRIGGER();
     const int t = items ? items[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     if (t < 0) return;                                  // padding of the item list
     const int pos = positions[t];

@@ -9,14 +9,22 @@
 // shared memory, which form o = O1 - lambda O2, normalise each row over vd and store it.
 //
 // Sizes are template arguments rounded up (dim to 32/64/128, vd to 32/64/128/256) with the padding columns
-// zero in shared memory; dim and vd themselves must be multiples of 8 (16-byte pieces).  Scores, the cap
-// (tanhf), the softmax and the final norm are float.
+// zero in shared memory; dim and vd themselves must be multiples of 8 (16-byte pieces).  Scores, the cap, the
+// softmax and the final norm are float; the cap's tanh and the weights' exponentials use the fast exp2.
 #include "diff_attention.cuh"
 #include "mma_sync.cuh"
 
 #define DT_ROWS 64      // query rows per block
 #define DT_KEYS 64      // keys per tile
 #define DT_THREADS 256
+
+// x: a score times log2(e); returns log2(e) * cap * tanh(score / cap) by tanh(y) = 1 - 2 / (1 + e^(2y)) with the
+// fast exponential and division (cap_l2 = log2(e) * cap, two_over_cap = 2 / cap_l2; cap_l2 <= 0: no cap)
+__device__ __forceinline__ float fast_cap(float x, float cap_l2, float two_over_cap) {
+    if (cap_l2 <= 0.f) return x;
+    const float e = fast_exp2(x * two_over_cap * 1.4426950408889634f);
+    return cap_l2 * (1.f - __fdividef(2.f, 1.f + e));
+}
 
 template <int DIMT, int VDT>
 struct DiffTileSmem {
@@ -35,23 +43,26 @@ __device__ __forceinline__ void load_kv_tile(bf16* stage, const bf16* __restrict
     bf16* sv = stage + DT_KEYS * L::K_LD;
     constexpr int KC = 2 * DIMT / 8, VC = VDT / 8;      // 16-byte pieces per row
     const int vd = cache.vd, ps = cache.page_size;
-    for (int idx = threadIdx.x; idx < DT_KEYS * (KC + VC); idx += DT_THREADS) {
-        const int row = idx / (KC + VC), c = idx % (KC + VC);
-        const int key = key0 + row;
-        int page = -1;
-        if (key >= lo && key <= hi) {
-            page = bt[key / ps];
-            if (page < 0 && status) *status = 1;        // a hole in the block table: the key counts as zeros
-        }
+    // four threads per key row: one look-up of the row's page, then the row's pieces in turn
+    const int row = threadIdx.x >> 2;
+    const int key = key0 + row;
+    int page = -1;
+    if (key >= lo && key <= hi) {
+        page = bt[key / ps];
+        if (page < 0 && status) *status = 1;            // a hole in the block table: the key counts as zeros
+    }
+    const bf16* krow = page >= 0 ? cache_keys(pool, cache, page, kvh, key % ps) : nullptr;
+    const bf16* vrow = page >= 0 ? cache_values(pool, cache, page, kvh, key % ps) : nullptr;
+    for (int c = threadIdx.x & 3; c < KC + VC; c += 4) {
         if (c < KC) {
             const int map = c / (DIMT / 8), e = (c % (DIMT / 8)) * 8;
             bf16* dst = sk + row * L::K_LD + map * DIMT + e;
-            if (page >= 0 && e < dim) cp_async16(dst, cache_keys(pool, cache, page, kvh, key % ps) + map * dim + e, true);
+            if (page >= 0 && e < dim) cp_async16(dst, krow + map * dim + e, true);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         } else {
             const int e = (c - KC) * 8;
             bf16* dst = sv + row * L::V_LD + e;
-            if (page >= 0 && e < vd) cp_async16(dst, cache_values(pool, cache, page, kvh, key % ps) + e, true);
+            if (page >= 0 && e < vd) cp_async16(dst, vrow + e, true);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
     }
@@ -68,6 +79,7 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     using L = DiffTileSmem<DIMT, VDT>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    ST_PDL_TRIGGER();
     const int tile = blockIdx.x / halves, part = blockIdx.x % halves;
     const int req = tiles[2 * tile], off = tiles[2 * tile + 1] + part * DT_ROWS;
     const int first = q_start[req], n_new = q_start[req + 1] - first;
@@ -112,6 +124,9 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 #pragma unroll
         for (int x = 0; x < 4; ++x) o[nt][x] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    // scores are kept in units of log2(e): s' = log2(e) * cap * tanh(scale * qk / cap), so that the weights are exp2
+    const float LOG2E = 1.4426950408889634f;
+    const float scale_l2 = scale * LOG2E, cap_l2 = cap * LOG2E, two_over_cap = cap > 0.f ? 2.f / cap_l2 : 0.f;
 
     const int kt_first = lo / DT_KEYS, kt_last = hi / DT_KEYS;
     load_kv_tile<DIMT, VDT>(smem, pool, cache, bt, kvh, kt_first * DT_KEYS, lo, hi, dim, status);
@@ -149,7 +164,7 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             for (int x = 0; x < 4; ++x) {
                 const int r = x >> 1, key = key0 + nt * 8 + 2 * tq + (x & 1);
                 const bool seen = live[r] && key >= vis[r] && key <= pos[r];
-                const float v = seen ? soft_cap(s[nt][x] * scale, cap) : -INFINITY;
+                const float v = seen ? fast_cap(s[nt][x] * scale_l2, cap_l2, two_over_cap) : -INFINITY;
                 s[nt][x] = v;
                 tmax[r] = fmaxf(tmax[r], v);
             }
@@ -159,7 +174,7 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
             tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
             const float m_new = fmaxf(m[r], tmax[r]);
-            corr[r] = m[r] == -INFINITY ? 0.f : expf(m[r] - m_new);
+            corr[r] = m[r] == -INFINITY ? 0.f : fast_exp2(m[r] - m_new);
             m[r] = m_new;
         }
         float tsum[2] = {0.f, 0.f};
@@ -170,7 +185,7 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
                 const int r = x >> 1;
-                p[x] = s[nt][x] == -INFINITY ? 0.f : expf(s[nt][x] - m[r]);
+                p[x] = s[nt][x] == -INFINITY ? 0.f : fast_exp2(s[nt][x] - m[r]);
                 tsum[r] += p[x];
             }
             pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p[0], p[1]);

@@ -102,9 +102,12 @@ hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
                   const int* __restrict__ positions, const int* __restrict__ q_start, const int* __restrict__ slots,
                   int nh, int dim, int vd) {
     using L = HcLayout<R>;
+    constexpr int DIMP = HC_LANES * R;                    // dim rounded up; 128 threads cover 128 / DIMP tokens a pass
+    constexpr int TOK_PASS = 128 / DIMP, PASSES = HG_GROUP / TOK_PASS;
     __shared__ __align__(16) float sq[HG_GROUP * L::ROW];
     __shared__ __align__(16) float sf[HG_GROUP * L::ROW];
     __shared__ float sv[HG_GROUP * HC_COLS];
+    ST_PDL_TRIGGER();
     const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * HC_COLS;
     const int first = q_start[b], n = q_start[b + 1] - first;
     if (n <= 0 || positions[first] < 0) return;           // padding of a fixed-shape step
@@ -117,29 +120,51 @@ hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
         const int i = l * R + r;
         S[r] = (i < dim && col < vd) ? st[(size_t)i * vd + col] : 0.f;
     }
+    // what this thread prepares of every group: row i of the gates and queries of the tokens k0, k0 + TOK_PASS, ...,
+    // and two values; the raw projections of the NEXT group are fetched before this group's recurrence runs
+    const int i_mine = tid % DIMP, k0 = tid / DIMP;
+    const bool row_live = i_mine < dim;
+    const float fb = row_live ? f_bias[h * dim + i_mine] : 0.f, lo = row_live ? lower[h * dim + i_mine] : 0.f;
+    const int at_mine = (i_mine / R) * L::LS + i_mine % R;
+    const int vk = tid / HC_COLS, vj = c0 + tid % HC_COLS;          // 128 threads: 8 tokens x 16 columns a pass
+    float zq[PASSES], zf[PASSES], zv[HG_GROUP / 8];
+    auto fetch = [&](int r0) {
+        const int rn = min(HG_GROUP, n - r0);
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int k = k0 + p * TOK_PASS;
+            zq[p] = zf[p] = 0.f;
+            if (k < rn && row_live) {
+                const T* row = proj + (size_t)(first + r0 + k) * ld + h * dim + i_mine;
+                zq[p] = to_f32(row[q_off]);
+                zf[p] = to_f32(row[f_off]);
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < HG_GROUP / 8; ++p) {
+            const int k = vk + p * 8;
+            zv[p] = (k < rn && vj < vd) ? to_f32(proj[(size_t)(first + r0 + k) * ld + v_off + h * vd + vj]) : 0.f;
+        }
+    };
+    fetch(0);
     for (int r0 = 0; r0 < n; r0 += HG_GROUP) {
         const int rn = min(HG_GROUP, n - r0);
-        __syncthreads();
-        for (int e = tid; e < rn * HC_LANES * R; e += 128) {
-            const int k = e / (HC_LANES * R), i = e % (HC_LANES * R);
-            float qv = 0.f, fv = 1.f;                         // rows past dim: nothing written, nothing read
-            if (i < dim) {
-                const T* row = proj + (size_t)(first + r0 + k) * ld;
-                const float zq = to_f32(row[q_off + h * dim + i]);
-                const float zf = to_f32(row[f_off + h * dim + i]) + f_bias[h * dim + i];
-                const float lo = lower[h * dim + i];
-                qv = zq / (1.f + expf(-zq));
-                fv = lo + (1.f - lo) * (1.f / (1.f + expf(-zf)));
+        __syncthreads();                                  // the group before has been read
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int k = k0 + p * TOK_PASS;
+            float qv = 0.f, fv = 1.f;                     // rows past dim: nothing written, nothing read
+            if (row_live) {
+                qv = zq[p] / (1.f + expf(-zq[p]));
+                fv = lo + (1.f - lo) * (1.f / (1.f + expf(-(zf[p] + fb))));
             }
-            const int at = k * L::ROW + (i / R) * L::LS + i % R;
-            sq[at] = qv;
-            sf[at] = fv;
+            sq[k * L::ROW + at_mine] = qv;
+            sf[k * L::ROW + at_mine] = fv;
         }
-        for (int e = tid; e < rn * HC_COLS; e += 128) {
-            const int k = e / HC_COLS, j = c0 + e % HC_COLS;
-            sv[e] = j < vd ? to_f32(proj[(size_t)(first + r0 + k) * ld + v_off + h * vd + j]) : 0.f;
-        }
+#pragma unroll
+        for (int p = 0; p < HG_GROUP / 8; ++p) sv[(vk + p * 8) * HC_COLS + tid % HC_COLS] = zv[p];
         __syncthreads();
+        if (r0 + HG_GROUP < n) fetch(r0 + HG_GROUP);
         for (int k = 0; k < rn; ++k) {
             const float v = sv[k * HC_COLS + warp * 4 + (lane & 3)];
             const float* fp = sf + k * L::ROW + l * L::LS;
@@ -179,6 +204,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 hgrn2_norm_kernel(const float* __restrict__ o_raw, const float* __restrict__ norm_w, float eps, T* __restrict__ out,
                   const int* __restrict__ positions, int n_tokens, int nh, int vd) {
+    ST_PDL_TRIGGER();
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (unit >= n_tokens * nh || positions[unit / nh] < 0) return;
     const float* row = o_raw + (size_t)unit * vd;

@@ -22,43 +22,76 @@
 
 #define CONV_MAX_TAPS 8
 
-// out[t][c] = (residual ? in[t][c] : 0) + conv(in)[t][c];  in: float residual rows or activations
-template <typename TI, typename TO>
-__global__ void __launch_bounds__(256)
+template <int V, typename T> __device__ __forceinline__ void load_v(const T* p, float* v) {
+    if (V == 4) { const float4 f = load4(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+    else v[0] = to_f32(p[0]);
+}
+template <int V, typename T> __device__ __forceinline__ void store_v(T* p, const float* v) {
+    if (V == 4) store4(p, make_float4(v[0], v[1], v[2], v[3]));
+    else p[0] = from_f32<T>(v[0]);
+}
+
+// out[t][c] = (residual ? in[t][c] : 0) + conv(in)[t][c];  in: float residual rows or activations.
+// A thread owns V neighbouring channels (V = 4: 16-byte accesses, channels % 4 == 0).
+template <typename TI, typename TO, int V>
+__global__ void __launch_bounds__(128)
 conv_residual_kernel(const TI* __restrict__ in, const float* __restrict__ w, float* __restrict__ state,
                      TO* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                      const int* __restrict__ q_start, const int* __restrict__ slots, int channels, int taps,
                      int residual) {
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    ST_PDL_TRIGGER();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     const int t = blockIdx.x;
     if (c >= channels || positions[t] < 0) return;      // padding token of a fixed-shape step
     const int b = seq_of_token[t];
     const int first = q_start[b], n = q_start[b + 1] - first, i = t - first;
     const int keep = taps - 1;
-    float wv[CONV_MAX_TAPS];
-    for (int j = 0; j < taps; ++j) wv[j] = w[(size_t)c * taps + j];
+    float wv[V][CONV_MAX_TAPS];
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+        for (int j = 0; j < taps; ++j) wv[v][j] = w[(size_t)(c + v) * taps + j];
     if (i >= keep) {
-        float y = 0.f;
-        for (int j = 0; j < taps; ++j) y = fmaf(wv[j], to_f32(in[(size_t)(t - keep + j) * channels + c]), y);
-        out[(size_t)t * channels + c] = from_f32<TO>((residual ? to_f32(in[(size_t)t * channels + c]) : 0.f) + y);
+        float y[V], x[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) y[v] = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            load_v<V>(in + (size_t)(t - keep + j) * channels + c, x);
+#pragma unroll
+            for (int v = 0; v < V; ++v) y[v] = fmaf(wv[v][j], x[v], y[v]);
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) y[v] += residual ? x[v] : 0.f;      // x holds the token's own row (j = taps - 1)
+        store_v<V>(out + (size_t)t * channels + c, y);
         return;
     }
     if (i != 0) return;                                 // done by the thread of the request's first token
     // u = old state followed by the first rows of the step: u[keep + k] is the step's token k
     float* st = state + (size_t)slots[b] * keep * channels + c;
-    float u[2 * CONV_MAX_TAPS];
+    float u[2 * CONV_MAX_TAPS][V];
     const int m = n < keep ? n : keep;                  // tokens that read the state
-    for (int j = 0; j < keep; ++j) u[j] = st[(size_t)j * channels];
-    for (int k = 0; k < m; ++k) u[keep + k] = to_f32(in[(size_t)(first + k) * channels + c]);
+    for (int j = 0; j < keep; ++j) load_v<V>(st + (size_t)j * channels, u[j]);
+    for (int k = 0; k < m; ++k) load_v<V>(in + (size_t)(first + k) * channels + c, u[keep + k]);
     for (int k = 0; k < m; ++k) {
-        float y = 0.f;
-        for (int j = 0; j < taps; ++j) y = fmaf(wv[j], u[k + j], y);
-        out[(size_t)(first + k) * channels + c] = from_f32<TO>((residual ? u[keep + k] : 0.f) + y);
+        float y[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            y[v] = 0.f;
+            for (int j = 0; j < taps; ++j) y[v] = fmaf(wv[v][j], u[k + j][v], y[v]);
+            y[v] += residual ? u[keep + k][v] : 0.f;
+        }
+        store_v<V>(out + (size_t)(first + k) * channels + c, y);
     }
     // the last `keep` inputs of old state + all n rows
     for (int j = 0; j < keep; ++j) {
         const int src = n + j;                          // index into (state, rows of the step)
-        st[(size_t)j * channels] = src < keep ? u[src] : to_f32(in[(size_t)(first + src - keep) * channels + c]);
+        float x[V];
+        if (src < keep) {
+#pragma unroll
+            for (int v = 0; v < V; ++v) x[v] = u[src][v];
+        } else {
+            load_v<V>(in + (size_t)(first + src - keep) * channels + c, x);
+        }
+        store_v<V>(st + (size_t)j * channels, x);
     }
 }
 
@@ -92,9 +125,16 @@ ST_EXPORT int st_conv_residual(const void* in, int in_f32, const float* w, float
     if (taps > CONV_MAX_TAPS) return ST_ERR_TOO_LARGE;
     if (dtype != 0 && dtype != 1) return ST_ERR_BAD_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(n_tokens, (channels + 255) / 256);
-#define CONV_LAUNCH(TI, TO) conv_residual_kernel<TI, TO><<<grid, 256, 0, s>>>((const TI*)in, w, state, (TO*)out, positions, \
-        seq_of_token, q_start, slots, channels, taps, residual)
+    const bool vec = channels % 4 == 0 && aligned16(in) && aligned16(out) && aligned16(state);
+    const int per_block = vec ? 128 * 4 : 128;
+    dim3 grid(n_tokens, (channels + per_block - 1) / per_block);
+#define CONV_LAUNCH(TI, TO)                                                                                           \
+    do {                                                                                                              \
+        if (vec) conv_residual_kernel<TI, TO, 4><<<grid, 128, 0, s>>>((const TI*)in, w, state, (TO*)out, positions,   \
+                                                                     seq_of_token, q_start, slots, channels, taps, residual); \
+        else conv_residual_kernel<TI, TO, 1><<<grid, 128, 0, s>>>((const TI*)in, w, state, (TO*)out, positions,       \
+                                                                  seq_of_token, q_start, slots, channels, taps, residual);    \
+    } while (0)
     if (dtype == 0) CONV_LAUNCH(float, float);
     else if (in_f32) CONV_LAUNCH(float, bf16);
     else CONV_LAUNCH(bf16, bf16);

@@ -73,6 +73,7 @@ class StepContext:
         self.act_dtype: torch.dtype = torch.float32
         self.device: Optional[torch.device] = None
         self.nvtx = False                # the model wraps every layer in an NVTX range
+        self.single_tokens = False       # every request of the step brings exactly one token (padding aside)
         self._plans: Dict[str, Any] = {}
         self._scratch_owner: Any = None
 
@@ -137,6 +138,7 @@ class _RecordedStep:
         self.lay = lay = runner._layout(n_cap, b_cap, w_cap)
         self.staging = _Staging(lay["total"], runner.device)
         self.ctx = runner._context_over(self.staging.dev, lay, n_cap, b_cap, w_cap, plan_keys, weakref.proxy(self))
+        self.ctx.single_tokens = decode
         self.token_from = self._view("token_from")
         if decode:
             assert n_cap == b_cap == w_cap
@@ -509,4 +511,5 @@ class ModelRunner:
         ctx.h_q_start, ctx.h_start_pos = info["q_start"].tolist(), info["start"].tolist()
         ctx.h_kv_len = [s + int(n) for s, n in zip(ctx.h_start_pos, info["lens"])]
         ctx.h_slots = [e.slot for e in entries]
+        ctx.single_tokens = N == B
         return ctx

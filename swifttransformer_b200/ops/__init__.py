@@ -744,17 +744,20 @@ def diff_qkv_prepare(proj: torch.Tensor, conv_w: torch.Tensor, conv_state: torch
                      k_norm: torch.Tensor, eps: float, inv_freq: torch.Tensor, rot_dims: int, q_out: torch.Tensor,
                      pool: torch.Tensor, layer: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
                      q_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int,
-                     dim: int, vd: int, page_size: int, status: torch.Tensor, write_kv: bool = True) -> None:
+                     dim: int, vd: int, page_size: int, status: torch.Tensor, write_kv: bool = True,
+                     move_state: bool = False) -> None:
     """From the fused projection q | k | v of the step's tokens: the short convolution over time of every channel
     (reading, not moving, the requests' last inputs in ``conv_state``), RMS norm of each map of each query and key
     head with the shared weights, rotation of the first ``rot_dims`` dimensions in neighbouring pairs by
-    position * inv_freq, queries to ``q_out`` [tokens, nh * 2 * dim], keys and values into their pages."""
+    position * inv_freq, queries to ``q_out`` [tokens, nh * 2 * dim], keys and values into their pages.
+    ``move_state``: only for steps in which every request brings exactly one token: the kernel then moves
+    ``conv_state`` on itself and ``conv_state_update`` is not needed."""
     taps = conv_w.shape[1]
     channels = (nh + nkv) * 2 * dim + nkv * vd
     assert proj.is_contiguous() and proj.shape[1] == channels and conv_w.shape == (channels, taps)
     assert conv_state.shape[1:] == (taps - 1, channels) and pool.dtype == proj.dtype == q_out.dtype
     stride, offset = _flat_pool(pool, layer, nkv, dim, vd, page_size)
-    _check(lib().st_diff_qkv_prepare(_p(proj), proj.shape[1], _p(conv_w), _p(conv_state), taps, _p(q_norm), _p(k_norm),
+    _check(lib().st_diff_qkv_prepare(_p(proj), proj.shape[1], _p(conv_w), _p(conv_state), int(move_state), taps, _p(q_norm), _p(k_norm),
                                      _f(eps), _p(inv_freq), rot_dims, _p(q_out), _p(pool), stride, offset,
                                      _p(positions), _p(seq_of_token), _p(q_start), _p(slots), _p(block_table),
                                      block_table.shape[1], proj.shape[0], nh, nkv, dim, vd, page_size, int(write_kv),

@@ -84,14 +84,16 @@ class DifferentialAttention(Mixer):
         n = h.shape[0]
         proj = ops.linear(h, self.w_qkv)
         q = torch.empty((n, self.qw), dtype=h.dtype, device=h.device)
+        # a step of single tokens (decoding): the preparation kernel moves the convolution's state itself
+        single = bool(getattr(ctx, "single_tokens", False))
         rot = self.qk_position
         rot_dims = rot.dims if rot is not None else 0
         inv_freq = rot.inv_freq(h.device) if rot is not None else self.q_norm
         ops.diff_qkv_prepare(proj, self.conv_w, tails.state, self.q_norm, self.k_norm, self.eps, inv_freq, rot_dims,
                              q, kv.pool, kv.layer, ctx.positions, ctx.seq_of_token, ctx.q_start, ctx.slots,
                              kv.block_table, self.nh, self.nkv, self.dim, self.vdim, kv.page_size, ctx.status,
-                             write_kv=kv.writable)
-        if self.taps > 1 and tails.writable:
+                             write_kv=kv.writable, move_state=single and tails.writable)
+        if self.taps > 1 and tails.writable and not single:
             ops.conv_state_update(proj, self.qw + self.kw + self.vw, tails.state, ctx.positions, ctx.q_start, ctx.slots,
                                   ctx.n_seqs)
         o = torch.empty((n, self.nh * self.vdim), dtype=h.dtype, device=h.device)
