@@ -114,7 +114,7 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             const int row = row0 + g + 8 * r;
             uint32_t v = 0;
             if (live[r] && col < dim)
-                v = *reinterpret_cast<const uint32_t*>(q + ((size_t)(first + off + row) * nh + h) * 2 * dim + map * dim + col);
+                v = __ldcg(reinterpret_cast<const uint32_t*>(q + ((size_t)(first + off + row) * nh + h) * 2 * dim + map * dim + col));
             qa[ks][x] = v;
         }
 

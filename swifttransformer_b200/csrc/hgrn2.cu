@@ -82,52 +82,55 @@ hgrn2_scan_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
 }
 
 // ------------------------------------------------------------------------------------------------
-// The same recurrence with the state in registers and the work of a head spread over blocks: a block owns
-// HC_COLS columns of S for one (request, head); eight lanes share a column, each with R consecutive rows of
-// it in registers (dim <= 8 R), and meet by shuffles for o = S^T q.  A warp owns four columns.  The blocks of
-// a head cannot normalise its output (each sees a slice of it): they leave o in float and
+// The same recurrence with the state in registers and the work of a head spread over blocks: a block of four
+// warps owns a few columns of S for one (request, head); LANES lanes (8 or 32) share a column, each with R
+// consecutive rows of it in registers (dim <= LANES * R), and meet by shuffles for o = S^T q.  Many small blocks:
+// every step of the recurrence waits for the one before, and only other warps on the same scheduler hide that.
+// The blocks of a head cannot normalise its output (each sees a slice of it): they leave o in float and
 // `hgrn2_norm_kernel` follows.  Per token the order of the sums is fixed, whatever the portion or the batch.
-#define HC_COLS 16
-#define HC_LANES 8
-
-template <int R> struct HcLayout {
-    static constexpr int LS = R >= 4 ? R + 4 : R + 1;       // floats between the rows of consecutive lanes (bank spread)
-    static constexpr int ROW = HC_LANES * LS;               // floats per token
+template <int R, int LANES> struct HcLayout {
+    static constexpr int CPW = 32 / LANES;                  // columns a warp owns
+    static constexpr int COLS = 4 * CPW;                    // columns a block (four warps) owns
+    static constexpr int LS = R == 4 ? 4 : (R > 4 ? R + 4 : R + 1);   // floats between consecutive lanes' rows (bank spread)
+    static constexpr int ROW = LANES * LS;                  // floats per token
+    static constexpr int DIMP = LANES * R;                  // dim rounded up
 };
 
-template <typename T, int R>
+template <typename T, int R, int LANES>
 __global__ void __launch_bounds__(128)
 hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int v_off, const float* __restrict__ f_bias,
-                  const float* __restrict__ lower, float* __restrict__ state, float* __restrict__ o_raw,
-                  const int* __restrict__ positions, const int* __restrict__ q_start, const int* __restrict__ slots,
-                  int nh, int dim, int vd) {
-    using L = HcLayout<R>;
-    constexpr int DIMP = HC_LANES * R;                    // dim rounded up; 128 threads cover 128 / DIMP tokens a pass
-    constexpr int TOK_PASS = 128 / DIMP, PASSES = HG_GROUP / TOK_PASS;
+                  const float* __restrict__ lower, const float* __restrict__ gates, float* __restrict__ state,
+                  float* __restrict__ o_raw, const int* __restrict__ positions, const int* __restrict__ q_start,
+                  const int* __restrict__ slots, int nh, int dim, int vd) {
+    using L = HcLayout<R, LANES>;
+    constexpr int DIMP = L::DIMP, COLS = L::COLS, CPW = L::CPW;
+    constexpr int TOK_PASS = 128 / DIMP, PASSES = HG_GROUP / TOK_PASS;      // 128 threads cover 128 / DIMP tokens a pass
+    constexpr int VTOK = 128 / COLS, VPASSES = VTOK >= HG_GROUP ? 1 : HG_GROUP / VTOK;
     __shared__ __align__(16) float sq[HG_GROUP * L::ROW];
     __shared__ __align__(16) float sf[HG_GROUP * L::ROW];
-    __shared__ float sv[HG_GROUP * HC_COLS];
+    __shared__ float sv[HG_GROUP * COLS];
+    ST_PDL_WAIT();
     ST_PDL_TRIGGER();
-    const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * HC_COLS;
+    const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
     const int first = q_start[b], n = q_start[b + 1] - first;
     if (n <= 0 || positions[first] < 0) return;           // padding of a fixed-shape step
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int l = lane >> 2, col = c0 + warp * 4 + (lane & 3);
+    const int l = lane / CPW, cw = warp * CPW + lane % CPW, col = c0 + cw;
     float* st = state + ((size_t)slots[b] * nh + h) * dim * vd;
     float S[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int i = l * R + r;
-        S[r] = (i < dim && col < vd) ? st[(size_t)i * vd + col] : 0.f;
+        S[r] = (i < dim && col < vd) ? __ldcg(st + (size_t)i * vd + col) : 0.f;
     }
     // what this thread prepares of every group: row i of the gates and queries of the tokens k0, k0 + TOK_PASS, ...,
-    // and two values; the raw projections of the NEXT group are fetched before this group's recurrence runs
+    // and some values; the raw projections of the NEXT group are fetched before this group's recurrence runs
     const int i_mine = tid % DIMP, k0 = tid / DIMP;
     const bool row_live = i_mine < dim;
     const float fb = row_live ? f_bias[h * dim + i_mine] : 0.f, lo = row_live ? lower[h * dim + i_mine] : 0.f;
     const int at_mine = (i_mine / R) * L::LS + i_mine % R;
-    const int vk = tid / HC_COLS, vj = c0 + tid % HC_COLS;          // 128 threads: 8 tokens x 16 columns a pass
-    float zq[PASSES], zf[PASSES], zv[HG_GROUP / 8];
+    const int vk = tid / COLS, vj = c0 + tid % COLS;
+    float zq[PASSES], zf[PASSES], zv[VPASSES];
     auto fetch = [&](int r0) {
         const int rn = min(HG_GROUP, n - r0);
 #pragma unroll
@@ -135,15 +138,21 @@ hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
             const int k = k0 + p * TOK_PASS;
             zq[p] = zf[p] = 0.f;
             if (k < rn && row_live) {
-                const T* row = proj + (size_t)(first + r0 + k) * ld + h * dim + i_mine;
-                zq[p] = to_f32(row[q_off]);
-                zf[p] = to_f32(row[f_off]);
+                if (gates) {                                  // silu(q) and the gate, prepared for all tokens at once
+                    const float* grow = gates + (size_t)(first + r0 + k) * 2 * nh * dim + h * dim + i_mine;
+                    zq[p] = __ldcg(grow);
+                    zf[p] = __ldcg(grow + nh * dim);
+                } else {
+                    const T* row = proj + (size_t)(first + r0 + k) * ld + h * dim + i_mine;
+                    zq[p] = load1_cg(row + q_off);              // through L2 only: the product just before wrote them
+                    zf[p] = load1_cg(row + f_off);
+                }
             }
         }
 #pragma unroll
-        for (int p = 0; p < HG_GROUP / 8; ++p) {
-            const int k = vk + p * 8;
-            zv[p] = (k < rn && vj < vd) ? to_f32(proj[(size_t)(first + r0 + k) * ld + v_off + h * vd + vj]) : 0.f;
+        for (int p = 0; p < VPASSES; ++p) {
+            const int k = vk + p * VTOK;
+            zv[p] = (k < rn && vj < vd) ? load1_cg(proj + (size_t)(first + r0 + k) * ld + v_off + h * vd + vj) : 0.f;
         }
     };
     fetch(0);
@@ -154,7 +163,10 @@ hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
         for (int p = 0; p < PASSES; ++p) {
             const int k = k0 + p * TOK_PASS;
             float qv = 0.f, fv = 1.f;                     // rows past dim: nothing written, nothing read
-            if (row_live) {
+            if (row_live && gates) {
+                qv = zq[p];
+                fv = zf[p];
+            } else if (row_live) {
                 qv = zq[p] / (1.f + expf(-zq[p]));
                 fv = lo + (1.f - lo) * (1.f / (1.f + expf(-(zf[p] + fb))));
             }
@@ -162,11 +174,13 @@ hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
             sf[k * L::ROW + at_mine] = fv;
         }
 #pragma unroll
-        for (int p = 0; p < HG_GROUP / 8; ++p) sv[(vk + p * 8) * HC_COLS + tid % HC_COLS] = zv[p];
+        for (int p = 0; p < VPASSES; ++p)
+            if (vk + p * VTOK < HG_GROUP) sv[(vk + p * VTOK) * COLS + tid % COLS] = zv[p];
         __syncthreads();
         if (r0 + HG_GROUP < n) fetch(r0 + HG_GROUP);
+#pragma unroll 4
         for (int k = 0; k < rn; ++k) {
-            const float v = sv[k * HC_COLS + warp * 4 + (lane & 3)];
+            const float v = sv[k * COLS + cw];
             const float* fp = sf + k * L::ROW + l * L::LS;
             const float* qp = sq + k * L::ROW + l * L::LS;
             float f[R], qq[R];
@@ -180,15 +194,16 @@ hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
 #pragma unroll
                 for (int r = 0; r < R; ++r) { f[r] = fp[r]; qq[r] = qp[r]; }
             }
-            float o = 0.f;
+            float o = 0.f, o2 = 0.f;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                S[r] = fmaf(f[r], S[r], (1.f - f[r]) * v);
-                o = fmaf(S[r], qq[r], o);
+                S[r] = fmaf(f[r], S[r] - v, v);               // f S + (1 - f) v
+                if (r & 1) o2 = fmaf(S[r], qq[r], o2);
+                else o = fmaf(S[r], qq[r], o);
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            o += __shfl_xor_sync(0xffffffffu, o, 8);
-            o += __shfl_xor_sync(0xffffffffu, o, 16);
+            o += o2;
+#pragma unroll
+            for (int d = CPW; d < 32; d <<= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
             if (l == 0 && col < vd) o_raw[((size_t)(first + r0 + k) * nh + h) * vd + col] = o;
         }
     }
@@ -199,20 +214,41 @@ hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
     }
 }
 
+// gates[t] = (silu(q projection) | lower + (1 - lower) sigmoid(gate projection + bias)) for every token and channel
+// at once: float [tokens, 2 * channels]; for long portions, where the recurrence's blocks would each repeat it
+template <typename T>
+__global__ void __launch_bounds__(256)
+hgrn2_gates_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, const float* __restrict__ f_bias,
+                   const float* __restrict__ lower, float* __restrict__ gates, const int* __restrict__ positions,
+                   int channels) {
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int t = blockIdx.x;
+    if (positions[t] < 0) return;
+    const T* row = proj + (size_t)t * ld;
+    float* g = gates + (size_t)t * 2 * channels;
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        const float zq = load1_cg(row + q_off + c), zf = load1_cg(row + f_off + c) + f_bias[c], lo = lower[c];
+        g[c] = zq / (1.f + expf(-zq));
+        g[channels + c] = lo + (1.f - lo) * (1.f / (1.f + expf(-zf)));
+    }
+}
+
 // out[t][h] = o_raw[t][h] / sqrt(mean(o_raw[t][h]^2) + eps) * norm_w, a warp per (token, head)
 template <typename T>
 __global__ void __launch_bounds__(256)
 hgrn2_norm_kernel(const float* __restrict__ o_raw, const float* __restrict__ norm_w, float eps, T* __restrict__ out,
                   const int* __restrict__ positions, int n_tokens, int nh, int vd) {
+    ST_PDL_WAIT();
     ST_PDL_TRIGGER();
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (unit >= n_tokens * nh || positions[unit / nh] < 0) return;
     const float* row = o_raw + (size_t)unit * vd;
     float ss = 0.f;
-    for (int j = lane; j < vd; j += 32) ss = fmaf(row[j], row[j], ss);
+    for (int j = lane; j < vd; j += 32) { const float v = __ldcg(row + j); ss = fmaf(v, v, ss); }
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)vd + eps);
-    for (int j = lane; j < vd; j += 32) out[(size_t)unit * vd + j] = from_f32<T>(row[j] * inv * norm_w[j]);
+    for (int j = lane; j < vd; j += 32) out[(size_t)unit * vd + j] = from_f32<T>(__ldcg(row + j) * inv * norm_w[j]);
 }
 
 static size_t hgrn2_smem(int dim, int vd) {
@@ -222,37 +258,56 @@ static size_t hgrn2_smem(int dim, int vd) {
 // proj: [tokens, ld] with the query, gate and value projections at column offsets q_off, f_off, v_off
 // state: [slots, nh, dim, vd] float; out: [tokens, nh * vd]
 // o_raw: float scratch [tokens, nh * vd] for the form with the state in registers (dim <= 128), or null for the
-// form with one block per head and the state in shared memory
+// form with one block per head and the state in shared memory; gates: float scratch [tokens, 2 * nh * dim] or null:
+// with it the gates and queries are prepared by a kernel of their own (worth it for long portions)
 ST_EXPORT int st_hgrn2_scan(const void* proj, int ld, int q_off, int f_off, int v_off, const float* f_bias,
                             const float* lower, const float* norm_w, float eps, float* state, void* out, float* o_raw,
-                            const int* positions, const int* q_start, const int* slots, int n_tokens, int n_seqs, int nh,
+                            float* gates, const int* positions, const int* q_start, const int* slots, int n_tokens, int n_seqs, int nh,
                             int dim, int vd, int dtype, void* stream) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (nh <= 0 || dim <= 0 || vd <= 0) return ST_ERR_BAD_ARG;
     if (dtype != 0 && dtype != 1) return ST_ERR_BAD_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
     if (o_raw && dim <= 128) {
-        dim3 grid(n_seqs, nh, (vd + HC_COLS - 1) / HC_COLS);
-#define HC_LAUNCH(T, R) hgrn2_cols_kernel<T, R><<<grid, 128, 0, s>>>((const T*)proj, ld, q_off, f_off, v_off, f_bias, lower,                                                                     state, o_raw, positions, q_start, slots, nh, dim, vd)
-#define HC_PICK(T)                                    \
-    do {                                              \
-        if (dim <= 8) HC_LAUNCH(T, 1);                \
-        else if (dim <= 16) HC_LAUNCH(T, 2);          \
-        else if (dim <= 32) HC_LAUNCH(T, 4);          \
-        else if (dim <= 64) HC_LAUNCH(T, 8);          \
-        else HC_LAUNCH(T, 16);                        \
+        if (gates) {
+            const int rc = dtype == 0
+                ? st_launch_pdl("hgrn2_gates", hgrn2_gates_kernel<float>, dim3(n_tokens), dim3(256), 0, s, (const float*)proj,
+                                ld, q_off, f_off, f_bias, lower, gates, positions, nh * dim)
+                : st_launch_pdl("hgrn2_gates", hgrn2_gates_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, (const bf16*)proj,
+                                ld, q_off, f_off, f_bias, lower, gates, positions, nh * dim);
+            if (rc) return rc;
+        }
+#define HC_LAUNCH(T, R, LANES)                                                                                        \
+    rc = st_launch_pdl("hgrn2_cols", hgrn2_cols_kernel<T, R, LANES>,                                                  \
+                       dim3(n_seqs, nh, (vd + HcLayout<R, LANES>::COLS - 1) / HcLayout<R, LANES>::COLS), dim3(128), 0, s, \
+                       (const T*)proj, ld, q_off, f_off, v_off, f_bias, lower, (const float*)gates, state, o_raw,     \
+                       positions, q_start, slots, nh, dim, vd)
+    // Long portions: a warp per column (many warps, each with little to do per token: the recurrence's steps wait
+    // for one another).  Steps of few tokens per request are bound by reading and writing the state: eight lanes
+    // per column, four columns side by side per warp, so that a row's piece is 16 bytes and not 4.
+    const bool long_portions = n_tokens > 4 * n_seqs;
+#define HC_PICK(T)                                                    \
+    do {                                                              \
+        if (dim <= 8) HC_LAUNCH(T, 1, 8);                             \
+        else if (dim <= 16) HC_LAUNCH(T, 2, 8);                       \
+        else if (dim <= 32 && long_portions) HC_LAUNCH(T, 1, 32);     \
+        else if (dim <= 32) HC_LAUNCH(T, 4, 8);                       \
+        else if (dim <= 64 && long_portions) HC_LAUNCH(T, 2, 32);     \
+        else if (dim <= 64) HC_LAUNCH(T, 8, 8);                       \
+        else if (long_portions) HC_LAUNCH(T, 4, 32);                  \
+        else HC_LAUNCH(T, 16, 8);                                     \
     } while (0)
+        int rc = 0;
         if (dtype == 0) HC_PICK(float); else HC_PICK(bf16);
 #undef HC_PICK
 #undef HC_LAUNCH
-        int rc = st_launch_status();
         if (rc) return rc;
         const int units = n_tokens * nh;
         if (dtype == 0)
-            hgrn2_norm_kernel<float><<<(units + 7) / 8, 256, 0, s>>>(o_raw, norm_w, eps, (float*)out, positions, n_tokens, nh, vd);
-        else
-            hgrn2_norm_kernel<bf16><<<(units + 7) / 8, 256, 0, s>>>(o_raw, norm_w, eps, (bf16*)out, positions, n_tokens, nh, vd);
-        return st_launch_status();
+            return st_launch_pdl("hgrn2_norm", hgrn2_norm_kernel<float>, dim3((units + 7) / 8), dim3(256), 0, s,
+                                 (const float*)o_raw, norm_w, eps, (float*)out, positions, n_tokens, nh, vd);
+        return st_launch_pdl("hgrn2_norm", hgrn2_norm_kernel<bf16>, dim3((units + 7) / 8), dim3(256), 0, s,
+                             (const float*)o_raw, norm_w, eps, (bf16*)out, positions, n_tokens, nh, vd);
     }
     const size_t smem = hgrn2_smem(dim, vd);
     if (smem > 200 * 1024) return ST_ERR_TOO_LARGE;

@@ -23,8 +23,9 @@
 #define CONV_MAX_TAPS 8
 
 template <int V, typename T> __device__ __forceinline__ void load_v(const T* p, float* v) {
-    if (V == 4) { const float4 f = load4(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
-    else v[0] = to_f32(p[0]);
+    // through L2 only: the rows were written by the kernel just before (see the note on programmatic launch)
+    if (V == 4) { const float4 f = load4_cg(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+    else v[0] = load1_cg(p);
 }
 template <int V, typename T> __device__ __forceinline__ void store_v(T* p, const float* v) {
     if (V == 4) store4(p, make_float4(v[0], v[1], v[2], v[3]));
@@ -39,17 +40,20 @@ conv_residual_kernel(const TI* __restrict__ in, const float* __restrict__ w, flo
                      TO* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                      const int* __restrict__ q_start, const int* __restrict__ slots, int channels, int taps,
                      int residual) {
-    ST_PDL_TRIGGER();
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     const int t = blockIdx.x;
+    float wv[V][CONV_MAX_TAPS];
+    if (c < channels) {                                 // the filters: no kernel writes them, fetched before the wait
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+            for (int j = 0; j < taps; ++j) wv[v][j] = w[(size_t)(c + v) * taps + j];
+    }
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
     if (c >= channels || positions[t] < 0) return;      // padding token of a fixed-shape step
     const int b = seq_of_token[t];
     const int first = q_start[b], n = q_start[b + 1] - first, i = t - first;
     const int keep = taps - 1;
-    float wv[V][CONV_MAX_TAPS];
-#pragma unroll
-    for (int v = 0; v < V; ++v)
-        for (int j = 0; j < taps; ++j) wv[v][j] = w[(size_t)(c + v) * taps + j];
     if (i >= keep) {
         float y[V], x[V];
 #pragma unroll
@@ -130,16 +134,15 @@ ST_EXPORT int st_conv_residual(const void* in, int in_f32, const float* w, float
     dim3 grid(n_tokens, (channels + per_block - 1) / per_block);
 #define CONV_LAUNCH(TI, TO)                                                                                           \
     do {                                                                                                              \
-        if (vec) conv_residual_kernel<TI, TO, 4><<<grid, 128, 0, s>>>((const TI*)in, w, state, (TO*)out, positions,   \
-                                                                     seq_of_token, q_start, slots, channels, taps, residual); \
-        else conv_residual_kernel<TI, TO, 1><<<grid, 128, 0, s>>>((const TI*)in, w, state, (TO*)out, positions,       \
-                                                                  seq_of_token, q_start, slots, channels, taps, residual);    \
+        if (vec) return st_launch_pdl("conv", conv_residual_kernel<TI, TO, 4>, grid, dim3(128), 0, s, (const TI*)in, w, state, \
+                                      (TO*)out, positions, seq_of_token, q_start, slots, channels, taps, residual);   \
+        return st_launch_pdl("conv", conv_residual_kernel<TI, TO, 1>, grid, dim3(128), 0, s, (const TI*)in, w, state, \
+                             (TO*)out, positions, seq_of_token, q_start, slots, channels, taps, residual);            \
     } while (0)
     if (dtype == 0) CONV_LAUNCH(float, float);
     else if (in_f32) CONV_LAUNCH(float, bf16);
     else CONV_LAUNCH(bf16, bf16);
 #undef CONV_LAUNCH
-    return st_launch_status();
 }
 
 // in: [rows, ld] of which the first `channels` columns are the convolution's inputs

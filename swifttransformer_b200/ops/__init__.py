@@ -783,6 +783,27 @@ def diff_attention_plain(q: torch.Tensor, pool: torch.Tensor, layer: int, out: t
     return out
 
 
+def diff_attention_single(q: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
+                          seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int,
+                          nkv: int, dim: int, vd: int, page_size: int, scale: float, cap: float, block: int,
+                          window: int, lam: float, eps: float, out_scale: float,
+                          status: Optional[torch.Tensor] = None, items: Optional[torch.Tensor] = None,
+                          n_items: int = 0) -> torch.Tensor:
+    """``diff_attention_plain`` for bfloat16 with 16-byte accesses (dim a multiple of 8 up to 128, vd a multiple of 4 up to 256): the
+    kernel for single tokens and short portions, bound by the way of the keys and values from memory.  Sizes it
+    does not take go to the plain kernel."""
+    if not (q.dtype == torch.bfloat16 and bool(lib().st_diff_attention_single_applies(dim, vd))):
+        return diff_attention_plain(q, pool, layer, out, positions, seq_of_token, slots, block_table, nh, nkv, dim, vd,
+                                    page_size, scale, cap, block, window, lam, eps, out_scale, status, items, n_items)
+    stride, offset = _flat_pool(pool, layer, nkv, dim, vd, page_size)
+    _check(lib().st_diff_attention_single(_p(q), _p(pool), stride, offset, _p(out), _p(items), _p(positions),
+                                          _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1],
+                                          n_items if items is not None else q.shape[0], nh, nkv, dim, vd, page_size,
+                                          _f(scale), _f(cap), block, window, _f(lam), _f(eps), _f(out_scale),
+                                          _p(status), _stream()), "diff_attention_single")
+    return out
+
+
 def diff_attention_tiles_applies(q: torch.Tensor, dim: int, vd: int) -> bool:
     """Whether the tensor-core kernel for prompt portions takes these sizes: bfloat16, dim and vd multiples of 8,
     dim <= 128, vd <= 256."""
@@ -807,6 +828,8 @@ def diff_attention_tiles(q: torch.Tensor, pool: torch.Tensor, layer: int, out: t
 
 
 # ------------------------------------------------------------ gated linear recurrence
+HGRN2_GATES_MIN_TOKENS = 64      # steps of more tokens prepare the recurrence's gates in a kernel of their own
+
 def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: torch.Tensor, lower: torch.Tensor,
                norm_w: torch.Tensor, eps: float, state: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                q_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, nh: int, dim: int, vd: int,
@@ -816,13 +839,19 @@ def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: t
     (1 - lower) sigmoid(gate + f_bias); out [tokens, nh * vd] = rms(o) * norm_w per head.  ``state``: float32
     [slots, nh, dim, vd], read and moved on.  ``scratch``: float32, at least tokens * nh * vd elements: with it (and
     dim <= 128) the state is carried in registers and a head's columns are spread over blocks; without it one block
-    per (request, head) keeps the state in shared memory."""
+    per (request, head) keeps the state in shared memory.  With room for tokens * nh * (vd + 2 * dim) elements and
+    more than HGRN2_GATES_MIN_TOKENS tokens, the gates and queries are prepared by a kernel of their own instead of
+    by every block of a head again."""
     assert proj.is_contiguous() and out.is_contiguous() and out.shape == (proj.shape[0], nh * vd)
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (nh, dim, vd)
+    gates = None
     if scratch is not None:
         assert scratch.dtype == torch.float32 and scratch.numel() >= out.numel()
+        n = proj.shape[0]
+        if n > HGRN2_GATES_MIN_TOKENS and scratch.numel() >= n * nh * (vd + 2 * dim):
+            gates = scratch[n * nh * vd:]
     _check(lib().st_hgrn2_scan(_p(proj), proj.shape[1], q_off, f_off, v_off, _p(f_bias), _p(lower), _p(norm_w),
-                               _f(eps), _p(state), _p(out), _p(scratch), _p(positions), _p(q_start), _p(slots),
+                               _f(eps), _p(state), _p(out), _p(scratch), _p(gates), _p(positions), _p(q_start), _p(slots),
                                proj.shape[0], n_seqs, nh, dim, vd, _dt(proj), _stream()), "hgrn2_scan")
     return out
 

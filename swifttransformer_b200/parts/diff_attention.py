@@ -107,9 +107,9 @@ class DifferentialAttention(Mixer):
                                          ctx.q_start, ctx.start_pos, ctx.slots, kv.block_table, *consts,
                                          status=ctx.status)
             if plan.n_items:
-                ops.diff_attention_plain(q, kv.pool, kv.layer, o, ctx.positions, ctx.seq_of_token, ctx.slots,
-                                         kv.block_table, *consts, status=ctx.status, items=plan.items,
-                                         n_items=plan.n_items)
+                ops.diff_attention_single(q, kv.pool, kv.layer, o, ctx.positions, ctx.seq_of_token, ctx.slots,
+                                          kv.block_table, *consts, status=ctx.status, items=plan.items,
+                                          n_items=plan.n_items)
         else:
             ops.diff_attention_plain(q, kv.pool, kv.layer, o, ctx.positions, ctx.seq_of_token, ctx.slots,
                                      kv.block_table, *consts, status=ctx.status)

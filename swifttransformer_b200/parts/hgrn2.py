@@ -51,7 +51,7 @@ class HGRN2(Mixer):
         o = torch.empty((h.shape[0], self.nh * self.vdim), dtype=h.dtype, device=h.device)
         ops.hgrn2_scan(proj, 0, qw, 2 * qw, self.f_bias, self.lower, self.norm_w, self.eps, cache.state, o,
                        ctx.positions, ctx.q_start, ctx.slots, ctx.n_seqs, self.nh, self.dim, self.vdim,
-                       scratch=ctx.scratch_f32(o.numel()) if self.dim <= 128 else None)
+                       scratch=ctx.scratch_f32(h.shape[0] * self.nh * (self.vdim + 2 * self.dim)) if self.dim <= 128 else None)
         return Delta(ops.linear(o, self.w_o))
 
     def param_bytes(self) -> int:

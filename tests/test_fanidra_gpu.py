@@ -128,10 +128,10 @@ def test_norm_add_and_gated_act(dtype, width):
 
 
 # ------------------------------------------------------------------------------------------ the recurrence
-@pytest.mark.parametrize("in_registers", [False, True])
+@pytest.mark.parametrize("in_registers", [False, True, "gates"])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,d,dv", [(2, 20, 40), (1, 64, 16), (3, 8, 130), (2, 128, 36), (1, 5, 7)])
-def test_hgrn2_scan_in_portions_and_token_by_token(dtype, H, d, dv, in_registers):
+def test_hgrn2_scan_in_portions_and_token_by_token(dtype, H, d, dv, in_registers, monkeypatch):
     from swifttransformer_b200 import ops
     rng = np.random.default_rng(H * 100 + d)
     T = 75
@@ -142,6 +142,8 @@ def test_hgrn2_scan_in_portions_and_token_by_token(dtype, H, d, dv, in_registers
     ref = pf.gated_recurrence(zq, zf, v, f_bias.astype(np.float32), lower.astype(np.float32),
                               norm_w.astype(np.float32), H, d, dv, 1e-5)
     proj = np.concatenate([zq, zf, v], axis=1)
+    if in_registers == "gates":
+        monkeypatch.setattr(ops, "HGRN2_GATES_MIN_TOKENS", 3)      # portions of four tokens and more prepare their gates
     for sizes in ((T,), (17, 2, 1, 1, 1, 30, 1, 1), (1,)):
         state = torch.zeros((3, H, d, dv), device="cuda")
         state[0].fill_(3.0)
@@ -152,7 +154,7 @@ def test_hgrn2_scan_in_portions_and_token_by_token(dtype, H, d, dv, in_registers
             out = torch.zeros((st.n_rows, H * dv), dtype=TD[dtype], device="cuda")
             ops.hgrn2_scan(rows, 0, H * d, 2 * H * d, dev(f_bias), dev(lower), dev(norm_w), 1e-5, state, out,
                            st.positions, st.q_start, st.slots, st.n_seqs, H, d, dv,
-                           scratch=torch.full((st.n_rows * H * dv,), 9.0, device="cuda") if in_registers else None)
+                           scratch=torch.full((st.n_rows * H * (dv + 2 * d),), 9.0, device="cuda") if in_registers else None)
             got[start:start + n] = out.float().cpu().numpy()[:n]
         assert torch.all(state[0] == 3.0) and torch.all(state[2] == 0.0)
         assert np.abs(got - ref).max() < (2e-5 if dtype == "float32" else 3e-2) * np.abs(ref).max(), sizes
@@ -233,8 +235,8 @@ class PagedHarness:
                 ops.diff_attention_tiles(q, self.pool, self.entry, out, ints(tiles), len(tiles), 128, st.q_start,
                                          ints([e[1] for e in entries] + [0]), st.slots, self.table, *consts,
                                          status=self.status)
-            ops.diff_attention_plain(q, self.pool, self.entry, out, st.positions, st.seq, st.slots, self.table, *consts,
-                                     status=self.status, items=ints(items), n_items=len(items))
+            ops.diff_attention_single(q, self.pool, self.entry, out, st.positions, st.seq, st.slots, self.table, *consts,
+                                      status=self.status, items=ints(items), n_items=len(items))
         else:
             ops.diff_attention_plain(q, self.pool, self.entry, out, st.positions, st.seq, st.slots, self.table, *consts,
                                      status=self.status)
@@ -473,9 +475,11 @@ def test_recorded_and_eager_steps_agree(fanidra_dirs, dtype):
         s = TraceSession(fanidra_dirs["mix"], dtype, helpers.live_token_need(steps), max_requests=2)
         s.runner.use_cuda_graphs = graphs
         outs.append(helpers.replay(s, steps))
+    # a recorded step has a padded shape, and the kernels choose their forms by shape (how many lanes share a column
+    # of the recurrence's state, which product kernel): the sums are the same, their order need not be
     for rid in reqs:
-        assert np.array_equal(outs[0][rid], outs[1][rid]) if dtype == "float32" else \
-            np.abs(outs[0][rid] - outs[1][rid]).max() < 2e-2 * np.abs(outs[1][rid]).max()
+        tol = 1e-5 if dtype == "float32" else 2e-2
+        assert np.abs(outs[0][rid] - outs[1][rid]).max() < tol * np.abs(outs[1][rid]).max()
 
 
 def test_block_mask_gives_pages_back_while_a_request_runs(fanidra_dirs):
