@@ -260,7 +260,7 @@ diff_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ pool,
 #define DA_QPASS 2      // and of the 2 * dim query / key elements: dim <= 128
 #define DA_THREADS 512  // sixteen warps: four per scheduler hide one another's waits (a block per SM is the usual launch)
 #define DA_WARPS (DA_THREADS / 32)
-#define DA_BATCH 2      // rows a warp asks for before it uses the first
+#define DA_BATCH (KT / DA_WARPS)   // a warp's keys of a tile: all their rows are asked for before the first is used
 
 __global__ void __launch_bounds__(DA_THREADS)
 diff_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, DiffCache cache,
@@ -354,6 +354,17 @@ diff_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict_
                 }
             }
         }
+        // the same keys' value rows are asked for now and wait in registers while the block does the softmax
+        float4 vv[DA_BATCH][DA_VPASS];
+#pragma unroll
+        for (int u = 0; u < DA_BATCH; ++u) {
+            const bf16* vr = srow[warp + DA_WARPS * u];
+#pragma unroll
+            for (int p = 0; p < DA_VPASS; ++p) {
+                const int e = p * 128 + 4 * lane;
+                vv[u][p] = (vr && e < vd) ? load4_cg(vr + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
         __syncthreads();
         const bool holds = threadIdx.x < KT;              // the softmax over the tile: a thread per key
         const float s1 = holds ? sp1[threadIdx.x] : -INFINITY, s2 = holds ? sp2[threadIdx.x] : -INFINITY;
@@ -372,32 +383,18 @@ diff_attention_single_kernel(const bf16* __restrict__ q, const bf16* __restrict_
         for (int p = 0; p < DA_VPASS; ++p)
 #pragma unroll
             for (int x = 0; x < 4; ++x) { a1[p][x] *= c1; a2[p][x] *= c2; }
-        const int j_end = min(KT, hi - base);
-        for (int jj0 = warp; jj0 < j_end; jj0 += DA_WARPS * DA_BATCH) {
-            float4 vv[DA_BATCH][DA_VPASS];
-            float w1[DA_BATCH], w2[DA_BATCH];
 #pragma unroll
-            for (int u = 0; u < DA_BATCH; ++u) {
-                const int jj = jj0 + DA_WARPS * u;
-                const bf16* vr = jj < j_end ? srow[jj] : nullptr;
-                w1[u] = vr ? sp1[jj] : 0.f;
-                w2[u] = vr ? sp2[jj] : 0.f;
+        for (int u = 0; u < DA_BATCH; ++u) {
+            const int jj = warp + DA_WARPS * u;
+            const float w1 = sp1[jj], w2 = sp2[jj];       // zero for a key that is not seen
 #pragma unroll
-                for (int p = 0; p < DA_VPASS; ++p) {
-                    const int e = p * 128 + 4 * lane;
-                    vv[u][p] = (vr && e < vd) ? load4_cg(vr + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+            for (int p = 0; p < DA_VPASS; ++p) {
+                const float4 v = vv[u][p];
+                a1[p][0] = fmaf(w1, v.x, a1[p][0]); a1[p][1] = fmaf(w1, v.y, a1[p][1]);
+                a1[p][2] = fmaf(w1, v.z, a1[p][2]); a1[p][3] = fmaf(w1, v.w, a1[p][3]);
+                a2[p][0] = fmaf(w2, v.x, a2[p][0]); a2[p][1] = fmaf(w2, v.y, a2[p][1]);
+                a2[p][2] = fmaf(w2, v.z, a2[p][2]); a2[p][3] = fmaf(w2, v.w, a2[p][3]);
             }
-#pragma unroll
-            for (int u = 0; u < DA_BATCH; ++u)
-#pragma unroll
-                for (int p = 0; p < DA_VPASS; ++p) {
-                    const float4 v = vv[u][p];
-                    a1[p][0] = fmaf(w1[u], v.x, a1[p][0]); a1[p][1] = fmaf(w1[u], v.y, a1[p][1]);
-                    a1[p][2] = fmaf(w1[u], v.z, a1[p][2]); a1[p][3] = fmaf(w1[u], v.w, a1[p][3]);
-                    a2[p][0] = fmaf(w2[u], v.x, a2[p][0]); a2[p][1] = fmaf(w2[u], v.y, a2[p][1]);
-                    a2[p][2] = fmaf(w2[u], v.z, a2[p][2]); a2[p][3] = fmaf(w2[u], v.w, a2[p][3]);
-                }
         }
         __syncthreads();
     }
