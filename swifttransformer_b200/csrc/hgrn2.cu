@@ -214,6 +214,141 @@ hgrn2_cols_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int 
     }
 }
 
+// The form for long portions: a warp owns FOUR neighbouring columns, all 32 lanes share each of them (R rows per
+// lane, dim <= 32 R).  The gates and queries a lane loads serve its four columns, the four column sums are reduced
+// together (the lanes pass on the half they do not keep: six shuffles for four sums), and the tokens of a group are
+// unrolled so that the chains of different tokens overlap: few warps with much to do each, where the warp per
+// column has many warps that each spend most instructions on loads and shuffles.
+#define HW_C 4
+
+template <typename T, int R>
+__global__ void __launch_bounds__(128)
+hgrn2_wide_kernel(const T* __restrict__ proj, int ld, int q_off, int f_off, int v_off, const float* __restrict__ f_bias,
+                  const float* __restrict__ lower, const float* __restrict__ gates, float* __restrict__ state,
+                  float* __restrict__ o_raw, const int* __restrict__ positions, const int* __restrict__ q_start,
+                  const int* __restrict__ slots, int nh, int dim, int vd) {
+    using L = HcLayout<R, 32>;
+    constexpr int DIMP = L::DIMP, COLS = 4 * HW_C;           // four warps, four columns each
+    constexpr int TOK_PASS = 128 / DIMP, PASSES = HG_GROUP / TOK_PASS;
+    constexpr int VTOK = 128 / COLS, VPASSES = HG_GROUP / VTOK;
+    __shared__ __align__(16) float sq[HG_GROUP * L::ROW];
+    __shared__ __align__(16) float sf[HG_GROUP * L::ROW];
+    __shared__ __align__(16) float sv[HG_GROUP * COLS];
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
+    const int first = q_start[b], n = q_start[b + 1] - first;
+    if (n <= 0 || positions[first] < 0) return;           // padding of a fixed-shape step
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int col0 = c0 + warp * HW_C;                    // the warp's first column
+    float* st = state + ((size_t)slots[b] * nh + h) * dim * vd;
+    float S[R][HW_C];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < HW_C; ++c) {
+            const int i = lane * R + r;
+            S[r][c] = (i < dim && col0 + c < vd) ? __ldcg(st + (size_t)i * vd + col0 + c) : 0.f;
+        }
+    const int i_mine = tid % DIMP, k0 = tid / DIMP;
+    const bool row_live = i_mine < dim;
+    const float fb = row_live ? f_bias[h * dim + i_mine] : 0.f, lo = row_live ? lower[h * dim + i_mine] : 0.f;
+    const int at_mine = (i_mine / R) * L::LS + i_mine % R;
+    const int vk = tid / COLS, vj = c0 + tid % COLS;
+    float zq[PASSES], zf[PASSES], zv[VPASSES];
+    auto fetch = [&](int r0) {
+        const int rn = min(HG_GROUP, n - r0);
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int k = k0 + p * TOK_PASS;
+            zq[p] = zf[p] = 0.f;
+            if (k < rn && row_live) {
+                if (gates) {
+                    const float* grow = gates + (size_t)(first + r0 + k) * 2 * nh * dim + h * dim + i_mine;
+                    zq[p] = __ldcg(grow);
+                    zf[p] = __ldcg(grow + nh * dim);
+                } else {
+                    const T* row = proj + (size_t)(first + r0 + k) * ld + h * dim + i_mine;
+                    zq[p] = load1_cg(row + q_off);
+                    zf[p] = load1_cg(row + f_off);
+                }
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < VPASSES; ++p) {
+            const int k = vk + p * VTOK;
+            zv[p] = (k < rn && vj < vd) ? load1_cg(proj + (size_t)(first + r0 + k) * ld + v_off + h * vd + vj) : 0.f;
+        }
+    };
+    fetch(0);
+    const bool up16 = lane & 16, up8 = lane & 8;
+    const int my_col = col0 + (up16 ? 2 : 0) + (up8 ? 1 : 0);   // the column whose sum this lane ends up with
+    for (int r0 = 0; r0 < n; r0 += HG_GROUP) {
+        const int rn = min(HG_GROUP, n - r0);
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int k = k0 + p * TOK_PASS;
+            float qv = 0.f, fv = 1.f;
+            if (row_live && gates) {
+                qv = zq[p];
+                fv = zf[p];
+            } else if (row_live) {
+                qv = zq[p] / (1.f + expf(-zq[p]));
+                fv = lo + (1.f - lo) * (1.f / (1.f + expf(-(zf[p] + fb))));
+            }
+            sq[k * L::ROW + at_mine] = qv;
+            sf[k * L::ROW + at_mine] = fv;
+        }
+#pragma unroll
+        for (int p = 0; p < VPASSES; ++p) sv[(vk + p * VTOK) * COLS + tid % COLS] = zv[p];
+        __syncthreads();
+        if (r0 + HG_GROUP < n) fetch(r0 + HG_GROUP);
+#pragma unroll 4
+        for (int k = 0; k < rn; ++k) {
+            const float4 v4 = *reinterpret_cast<const float4*>(sv + k * COLS + warp * HW_C);
+            const float v[HW_C] = {v4.x, v4.y, v4.z, v4.w};
+            const float* fp = sf + k * L::ROW + lane * L::LS;
+            const float* qp = sq + k * L::ROW + lane * L::LS;
+            float f[R], qq[R];
+            if (R % 4 == 0) {
+#pragma unroll
+                for (int r = 0; r < R; r += 4) {
+                    *reinterpret_cast<float4*>(f + r) = *reinterpret_cast<const float4*>(fp + r);
+                    *reinterpret_cast<float4*>(qq + r) = *reinterpret_cast<const float4*>(qp + r);
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) { f[r] = fp[r]; qq[r] = qp[r]; }
+            }
+            float o[HW_C] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int c = 0; c < HW_C; ++c) {
+                    S[r][c] = fmaf(f[r], S[r][c] - v[c], v[c]);       // f S + (1 - f) v
+                    o[c] = fmaf(S[r][c], qq[r], o[c]);
+                }
+            // four sums over 32 lanes: halves pass on the pair they do not keep, then quarters, then within eight lanes
+            const float g0 = __shfl_xor_sync(0xffffffffu, up16 ? o[0] : o[2], 16);
+            const float g1 = __shfl_xor_sync(0xffffffffu, up16 ? o[1] : o[3], 16);
+            const float a = (up16 ? o[2] : o[0]) + g0, bb = (up16 ? o[3] : o[1]) + g1;
+            float c1 = (up8 ? bb : a) + __shfl_xor_sync(0xffffffffu, up8 ? a : bb, 8);
+            c1 += __shfl_xor_sync(0xffffffffu, c1, 4);
+            c1 += __shfl_xor_sync(0xffffffffu, c1, 2);
+            c1 += __shfl_xor_sync(0xffffffffu, c1, 1);
+            if ((lane & 7) == 0 && my_col < vd) o_raw[((size_t)(first + r0 + k) * nh + h) * vd + my_col] = c1;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < HW_C; ++c) {
+            const int i = lane * R + r;
+            if (i < dim && col0 + c < vd) st[(size_t)i * vd + col0 + c] = S[r][c];
+        }
+}
+
 // gates[t] = (silu(q projection) | lower + (1 - lower) sigmoid(gate projection + bias)) for every token and channel
 // at once: float [tokens, 2 * channels]; for long portions, where the recurrence's blocks would each repeat it
 template <typename T>
@@ -282,25 +417,30 @@ ST_EXPORT int st_hgrn2_scan(const void* proj, int ld, int q_off, int f_off, int 
                        dim3(n_seqs, nh, (vd + HcLayout<R, LANES>::COLS - 1) / HcLayout<R, LANES>::COLS), dim3(128), 0, s, \
                        (const T*)proj, ld, q_off, f_off, v_off, f_bias, lower, (const float*)gates, state, o_raw,     \
                        positions, q_start, slots, nh, dim, vd)
-    // Long portions: a warp per column (many warps, each with little to do per token: the recurrence's steps wait
-    // for one another).  Steps of few tokens per request are bound by reading and writing the state: eight lanes
-    // per column, four columns side by side per warp, so that a row's piece is 16 bytes and not 4.
+    // Long portions: the wide form (32 lanes per column, four columns per warp).  Steps of few tokens per request
+    // are bound by reading and writing the state: eight lanes per column with many rows each, four columns side by
+    // side per warp.
     const bool long_portions = n_tokens > 4 * n_seqs;
+#define HW_LAUNCH(T, R)                                                                                               \
+    rc = st_launch_pdl("hgrn2_wide", hgrn2_wide_kernel<T, R>, dim3(n_seqs, nh, (vd + 4 * HW_C - 1) / (4 * HW_C)), dim3(128), \
+                       0, s, (const T*)proj, ld, q_off, f_off, v_off, f_bias, lower, (const float*)gates, state, o_raw, \
+                       positions, q_start, slots, nh, dim, vd)
 #define HC_PICK(T)                                                    \
     do {                                                              \
         if (dim <= 8) HC_LAUNCH(T, 1, 8);                             \
         else if (dim <= 16) HC_LAUNCH(T, 2, 8);                       \
-        else if (dim <= 32 && long_portions) HC_LAUNCH(T, 1, 32);     \
+        else if (dim <= 32 && long_portions) HW_LAUNCH(T, 1);         \
         else if (dim <= 32) HC_LAUNCH(T, 4, 8);                       \
-        else if (dim <= 64 && long_portions) HC_LAUNCH(T, 2, 32);     \
+        else if (dim <= 64 && long_portions) HW_LAUNCH(T, 2);         \
         else if (dim <= 64) HC_LAUNCH(T, 8, 8);                       \
-        else if (long_portions) HC_LAUNCH(T, 4, 32);                  \
+        else if (long_portions) HW_LAUNCH(T, 4);                      \
         else HC_LAUNCH(T, 16, 8);                                     \
     } while (0)
         int rc = 0;
         if (dtype == 0) HC_PICK(float); else HC_PICK(bf16);
 #undef HC_PICK
 #undef HC_LAUNCH
+#undef HW_LAUNCH
         if (rc) return rc;
         const int units = n_tokens * nh;
         if (dtype == 0)
