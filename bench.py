@@ -129,13 +129,13 @@ def compare_designs(args, peaks):
 
     def configs(z):
         att = {"type": "attention", "mlp": {"kind": "dense", "ff": z["ff"]},
-               "mixer": dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], conv=4,
-                             scale=z["dim"] ** -0.5, diff=0.3, softcap=50.0, mask={"size": z["block"]},
-                             rot={"dims": z["dim"], "base": 1e6})}
+               "mixer": dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], conv=3,
+                             scale=z["dim"] ** -0.5, diff=0.25, softcap=30.0, mask={"size": z["block"]},
+                             rot={"dims": z["dim"], "base": 10000.0})}
         rec = {"type": "hgrn2", "mlp": {"kind": "dense", "ff": z["ff"]},
                "mixer": dict(heads=z["rec_heads"], dim=z["rec_dim"], vdim=z["rec_vdim"])}
         fan = FanidraConfig.from_dict(dict(architecture="Fanidra", vocab=vocab, width=z["width"], norm={"eps": 1e-5},
-                                           residual_mult=0.3, embedding={"scale": 12.0}, canon={"taps": 3},
+                                           residual_mult=0.5, embedding={"scale": 8.0}, canon={"taps": 4},
                                            layers=[rec if i % 4 == 1 else att for i in range(n_layers)]))
         opt = OptConfig.from_dict(dict(vocab_size=vocab, hidden_size=z["width"], num_hidden_layers=n_layers,
                                        ffn_dim=z["opt_ffn"], num_attention_heads=z["opt_heads"],
