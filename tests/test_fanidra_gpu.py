@@ -524,3 +524,59 @@ def test_greedy_generation_through_the_engine(fanidra_dirs, name, dtype):
                 gap = logits[best] - logits[tok]
                 assert dtype == "bfloat16" and gap < 0.05 * np.abs(logits).max(), (name, k, tok, best, gap)
             toks.append(tok)
+
+
+# ------------------------------------------------------------------------------------------ the programs
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_run_gpt_takes_a_fanidra_folder(fanidra_dirs, tmp_path):
+    import subprocess
+    import sys
+    vocab = CONFIGS["mix"]["cfg"]["vocab"]
+    prompts = [helpers.random_tokens(vocab, n, 70 + n) for n in (6, 21)]
+    inp = tmp_path / "in.txt"
+    inp.write_text("\n".join(" ".join(map(str, p)) for p in prompts) + "\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "run_gpt"), fanidra_dirs["mix"], "any", "fp32", str(inp),
+                        "--max_decoding_step", "5", "--num_total_blocks", "32"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    cfg, w = pf.load_model(fanidra_dirs["mix"])
+    lines = [l for l in r.stdout.splitlines() if l.startswith("[")]
+    assert len(lines) == 2
+    for line, p in zip(lines, prompts):
+        got = [int(t) for t in line.split(")")[1].split("(")[0].split()]
+        toks = list(p)
+        for tok in got:
+            assert tok == int(np.argmax(pf.forward(cfg, w, toks)[-1]))
+            toks.append(tok)
+        assert len(got) == 5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program_with_four_slots(fanidra_dirs, tmp_path, dtype):
+    """bin/trace_run with its defaults (four request slots, pages of 16): six requests, at most four live, so slots and
+    pages are handed out again; every wanted row against the plain implementation."""
+    import subprocess
+    import sys
+    name = "mix"
+    reqs = requests_for(name, lengths=(50, 1, 33, 70, 18, 40))
+    steps = helpers.trace_mixed(reqs, seed=3, max_live=4)
+    out = tmp_path / "out"
+    p = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", fanidra_dirs[name], "--dtype", dtype,
+                          "--out", str(out), "--max-tokens", str(helpers.live_token_need(steps))],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    got = {rid: [] for rid in reqs}
+    vocab = CONFIGS[name]["cfg"]["vocab"]
+    for i, st in enumerate(steps):
+        p.stdin.write(json.dumps(dict(st, step=i)) + "\n")
+        p.stdin.flush()
+        assert p.stdout.readline().strip() == f"done {i}", p.stderr.read()[-2000:]
+        arr = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, vocab)
+        k = 0
+        for e in st["entries"]:
+            got[e["id"]].append(arr[k:k + len(e["want"])])
+            k += len(e["want"])
+        assert k == len(arr)
+    p.stdin.close()
+    assert p.wait(timeout=120) == 0
+    compare(fanidra_dirs[name], reqs, {rid: np.concatenate(v) for rid, v in got.items()}, dtype, "trace_run")
