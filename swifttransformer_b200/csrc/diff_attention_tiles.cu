@@ -104,6 +104,9 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         pos[r] = p_first + row;
         vis[r] = first_visible(pos[r], block, window);
     }
+    // what decides whether a key tile needs a mask for this warp's sixteen rows
+    const bool w_all_live = row0 + 15 < rows_here;
+    const int w_pos_min = p_first + row0, w_vis_max = first_visible(p_first + row0 + 15, block, window);
     // Q fragments of the warp's map, from global memory (once)
     uint32_t qa[DIMT / 16][4];
 #pragma unroll
@@ -156,18 +159,30 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                 mma_bf16(s[nt], qa[ks], b0, b1);
             }
         }
-        // scale, cap, mask; running maximum
+        // scale, cap, mask; running maximum.  A tile that lies wholly inside the range of every row of the warp
+        // needs no mask.
         float tmax[2] = {-INFINITY, -INFINITY};
+        if (w_all_live && key0 + DT_KEYS - 1 <= w_pos_min && key0 >= w_vis_max) {
 #pragma unroll
-        for (int nt = 0; nt < DT_KEYS / 8; ++nt)
+            for (int nt = 0; nt < DT_KEYS / 8; ++nt)
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const int r = x >> 1, key = key0 + nt * 8 + 2 * tq + (x & 1);
-                const bool seen = live[r] && key >= vis[r] && key <= pos[r];
-                const float v = seen ? fast_cap(s[nt][x] * scale_l2, cap_l2, two_over_cap) : -INFINITY;
-                s[nt][x] = v;
-                tmax[r] = fmaxf(tmax[r], v);
-            }
+                for (int x = 0; x < 4; ++x) {
+                    const float v = fast_cap(s[nt][x] * scale_l2, cap_l2, two_over_cap);
+                    s[nt][x] = v;
+                    tmax[x >> 1] = fmaxf(tmax[x >> 1], v);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < DT_KEYS / 8; ++nt)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const int r = x >> 1, key = key0 + nt * 8 + 2 * tq + (x & 1);
+                    const bool seen = live[r] && key >= vis[r] && key <= pos[r];
+                    const float v = seen ? fast_cap(s[nt][x] * scale_l2, cap_l2, two_over_cap) : -INFINITY;
+                    s[nt][x] = v;
+                    tmax[r] = fmaxf(tmax[r], v);
+                }
+        }
         float corr[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -197,10 +212,12 @@ diff_attention_tiles_kernel(const bf16* __restrict__ q, const bf16* __restrict__
             tsum[r] += __shfl_xor_sync(0xffffffffu, tsum[r], 2);
             l[r] = l[r] * corr[r] + tsum[r];
         }
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {     // a maximum of the warp's rows moved
 #pragma unroll
-        for (int nt = 0; nt < VDT / 8; ++nt) {
-            o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
-            o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+            for (int nt = 0; nt < VDT / 8; ++nt) {
+                o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
+                o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+            }
         }
         // O += P V: V [key][vd] is the k-major operand, read transposed
 #pragma unroll
