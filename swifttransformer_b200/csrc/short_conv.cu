@@ -46,7 +46,9 @@ conv_residual_kernel(const TI* __restrict__ in, const float* __restrict__ w, flo
     if (c < channels) {                                 // the filters: no kernel writes them, fetched before the wait
 #pragma unroll
         for (int v = 0; v < V; ++v)
-            for (int j = 0; j < taps; ++j) wv[v][j] = w[(size_t)(c + v) * taps + j];
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS; ++j)     // (constant bounds: the filters stay in registers)
+                wv[v][j] = j < taps ? w[(size_t)(c + v) * taps + j] : 0.f;
     }
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
@@ -58,10 +60,13 @@ conv_residual_kernel(const TI* __restrict__ in, const float* __restrict__ w, flo
         float y[V], x[V];
 #pragma unroll
         for (int v = 0; v < V; ++v) y[v] = 0.f;
-        for (int j = 0; j < taps; ++j) {
-            load_v<V>(in + (size_t)(t - keep + j) * channels + c, x);
 #pragma unroll
-            for (int v = 0; v < V; ++v) y[v] = fmaf(wv[v][j], x[v], y[v]);
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+            if (j < taps) {
+                load_v<V>(in + (size_t)(t - keep + j) * channels + c, x);
+#pragma unroll
+                for (int v = 0; v < V; ++v) y[v] = fmaf(wv[v][j], x[v], y[v]);
+            }
         }
 #pragma unroll
         for (int v = 0; v < V; ++v) y[v] += residual ? x[v] : 0.f;      // x holds the token's own row (j = taps - 1)
@@ -79,8 +84,8 @@ conv_residual_kernel(const TI* __restrict__ in, const float* __restrict__ w, flo
         float y[V];
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-            y[v] = 0.f;
-            for (int j = 0; j < taps; ++j) y[v] = fmaf(wv[v][j], u[k + j][v], y[v]);
+            y[v] = 0.f;      // (the filters once more from memory: indexing wv by a variable would move it out of registers)
+            for (int j = 0; j < taps; ++j) y[v] = fmaf(w[(size_t)(c + v) * taps + j], u[k + j][v], y[v]);
             y[v] += residual ? u[keep + k][v] : 0.f;
         }
         store_v<V>(out + (size_t)(first + k) * channels + c, y);
