@@ -1,0 +1,142 @@
+// Grouped matrix products: many products of the same shape of weights, each over its own rows.
+//
+//   c[row, g * c_goff + n] = epilogue( sum_k a[arow, g * a_goff + k] * w[g][n][k] )        w[g] stored [out, in]
+//
+// Two ways to say which rows a group has:
+//   * every group takes all n_rows rows (the heads of an attention layer, each with a matrix of its own on its own
+//     columns of a: a_goff / c_goff are the column offsets from one head to the next); grid.z walks the groups;
+//   * a group takes the rows offsets[g]..offsets[g+1]-1 of a sorted list (the experts of a mixture): the launch walks
+//     row tiles (tile_group[i], tile_row0[i]) made on the device, arow = a_rows[row] / a_row_div where a_rows is
+//     given (the sorted (token, choice) items, a_row_div choices per token), else the row itself.
+// Epilogue: none, or "gated": w[g] holds 2 * n_out rows, gate rows first, and c = act(gate) * up.
+//
+// gemm_grouped_plain: float arithmetic for either storage type; every output element is one chain of fused
+// multiply-adds over k in ascending order whatever rows share its tile (the 32-bit path, and the plain twin).
+#include "common.cuh"
+
+struct GroupedShape {
+    int n_rows, n_out, k_dim, gated, act;
+    long long lda, a_goff, ldc, c_goff, w_gstride;
+    const int* offsets;        // null: every group takes all rows
+    const int* tile_group;
+    const int* tile_row0;
+    const int* a_rows;
+    int a_row_div;
+};
+
+#define GG_BM 64
+#define GG_BN 64
+#define GG_BK 16
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+gemm_grouped_plain_kernel(const T* __restrict__ a, const T* __restrict__ w, TO* __restrict__ c, GroupedShape sh) {
+    __shared__ float sa[GG_BK][GG_BM + 4];
+    __shared__ float sw[GG_BK][GG_BN + 4];
+    __shared__ float su[GG_BK][GG_BN + 4];
+    __shared__ int srow[GG_BM];
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    int g, row0, row_end;
+    if (sh.offsets) {
+        g = __ldcg(sh.tile_group + blockIdx.y);
+        if (g < 0) return;
+        row0 = __ldcg(sh.tile_row0 + blockIdx.y);
+        row_end = min(row0 + GG_BM, __ldcg(sh.offsets + g + 1));
+    } else {
+        g = blockIdx.z;
+        row0 = blockIdx.y * GG_BM;
+        row_end = min(row0 + GG_BM, sh.n_rows);
+    }
+    if (threadIdx.x < GG_BM) {
+        const int r = row0 + threadIdx.x;
+        int ar = -1;
+        if (r < row_end) ar = sh.a_rows ? __ldcg(sh.a_rows + r) / sh.a_row_div : r;
+        srow[threadIdx.x] = ar;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int col0 = blockIdx.x * GG_BN;
+    const T* wg = w + (long long)g * sh.w_gstride;
+    float acc[4][4], acu[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = acu[i][j] = 0.f;
+    for (int k0 = 0; k0 < sh.k_dim; k0 += GG_BK) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = threadIdx.x + it * 256;
+            const int r = idx / GG_BK, kk = idx % GG_BK;
+            const int k = k0 + kk;
+            const int ar = srow[r], wr = col0 + r;
+            sa[kk][r] = (ar >= 0 && k < sh.k_dim) ? load1_cg(a + (long long)ar * sh.lda + g * sh.a_goff + k) : 0.f;
+            const bool ok = wr < sh.n_out && k < sh.k_dim;
+            sw[kk][r] = ok ? to_f32(wg[(long long)wr * sh.k_dim + k]) : 0.f;
+            if (sh.gated) su[kk][r] = ok ? to_f32(wg[(long long)(sh.n_out + wr) * sh.k_dim + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GG_BK; ++kk) {
+            float av[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = sa[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = sw[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+            if (sh.gated) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wv[j] = su[kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acu[i][j] = fmaf(av[i], wv[j], acu[i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = row0 + ty * 4 + i;
+        if (r >= row_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = col0 + tx * 4 + j;
+            if (n >= sh.n_out) continue;
+            float v = acc[i][j];
+            if (sh.gated) {
+                // both products are rounded to the storage type first, as two separate products would leave them
+                v = apply_act(to_f32(from_f32<T>(v)), sh.act) * to_f32(from_f32<T>(acu[i][j]));
+            }
+            c[(long long)r * sh.ldc + g * sh.c_goff + n] = from_f32<TO>(v);
+        }
+    }
+}
+
+ST_EXPORT int st_gemm_grouped_plain(const void* a, const void* w, void* c, int n_groups, int n_rows, int n_out, int k_dim,
+                                    int gated, int act, long long lda, long long a_goff, long long ldc, long long c_goff,
+                                    long long w_gstride, const int* offsets, const int* tile_group, const int* tile_row0,
+                                    int n_tiles, const int* a_rows, int a_row_div, int dtype, int out_f32, void* stream) {
+    if (n_groups <= 0 || n_out <= 0) return 0;
+    if (k_dim <= 0 || (offsets && (!tile_group || !tile_row0 || n_tiles <= 0)) || (a_rows && a_row_div <= 0)) return ST_ERR_BAD_ARG;
+    if (!offsets && n_rows <= 0) return 0;
+    GroupedShape sh{n_rows, n_out, k_dim, gated, act, lda, a_goff, ldc, c_goff, w_gstride, offsets, tile_group, tile_row0,
+                    a_rows, a_row_div};
+    dim3 grid((n_out + GG_BN - 1) / GG_BN, offsets ? n_tiles : (n_rows + GG_BM - 1) / GG_BM, offsets ? 1 : n_groups);
+    if (grid.y > 65535 || grid.z > 65535) return ST_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == 0)
+        return st_launch_pdl("gemm_grouped", gemm_grouped_plain_kernel<float, float>, grid, dim3(256), 0, s, (const float*)a,
+                             (const float*)w, (float*)c, sh);
+    if (dtype != 1) return ST_ERR_BAD_DTYPE;
+    if (out_f32)
+        return st_launch_pdl("gemm_grouped", gemm_grouped_plain_kernel<bf16, float>, grid, dim3(256), 0, s, (const bf16*)a,
+                             (const bf16*)w, (float*)c, sh);
+    return st_launch_pdl("gemm_grouped", gemm_grouped_plain_kernel<bf16, bf16>, grid, dim3(256), 0, s, (const bf16*)a,
+                         (const bf16*)w, (bf16*)c, sh);
+}
+
+ST_EXPORT int st_gemm_grouped_tile_rows() { return GG_BM; }

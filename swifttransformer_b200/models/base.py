@@ -29,8 +29,9 @@ from ..weights.spec import ParamSpec
 @dataclasses.dataclass(frozen=True)
 class LayerStep:
     block: int                  # index into ModelDef.blocks
-    cache: int                  # index of the cache entry this step uses
+    cache: int                  # index of the cache entry this step uses (-1: the block has no mixer and no cache)
     writes_cache: bool = True   # False: reads the entry another step fills
+    turn: int = 0               # for blocks that run once per pass over a stretch of shared layers: which pass
 
 
 @dataclasses.dataclass
@@ -88,6 +89,10 @@ class ModelDef:
         specs: List[Any] = [None] * self.num_cache_entries()
         owner = [False] * len(specs)
         for st in self.layer_order:
+            if st.cache < 0:
+                if self.blocks[st.block].mixer is not None:
+                    raise ValueError("a layer step without a cache entry runs a block with a mixer")
+                continue
             spec = self.blocks[st.block].mixer.cache_spec()
             if st.writes_cache:
                 if owner[st.cache]:
@@ -95,7 +100,7 @@ class ModelDef:
                 owner[st.cache] = True
                 specs[st.cache] = spec
         for st in self.layer_order:
-            if not st.writes_cache:
+            if not st.writes_cache and st.cache >= 0:
                 spec = self.blocks[st.block].mixer.cache_spec()
                 if not owner[st.cache]:
                     raise ValueError(f"cache entry {st.cache} is read but no layer step writes it")
@@ -118,6 +123,9 @@ class CausalLM:
         self.embedding, self.position = model_def.embedding, model_def.position
         self.blocks, self.layer_order = model_def.blocks, model_def.layer_order
         self.final_norm, self.head = model_def.final_norm, model_def.head
+        self._keeps_embedding = any(getattr(b, "wants_embedding", False) for b in self.blocks)
+        # a hook for tools that look at the residual stream: called with (layer step index, stream) after every step
+        self.after_layer: Optional[Callable[[int, Any], None]] = None
 
     @property
     def vocab_size(self) -> int:
@@ -131,13 +139,14 @@ class CausalLM:
         return min(limits) if limits else None
 
     def graph_safe(self) -> bool:
-        return all(b.mixer.graph_safe for b in self.blocks)
+        return all(b.mixer.graph_safe for b in self.blocks if b.mixer is not None)
 
     def step_plans(self) -> List[Any]:
         """The step plans (parts.base.StepPlan) of the model's mixers, one per name, in layer order."""
         plans: Dict[str, Any] = {}
         for st in self.layer_order:
-            p = self.blocks[st.block].mixer.step_plan()
+            mixer = self.blocks[st.block].mixer
+            p = mixer.step_plan() if mixer is not None else None
             if p is not None and p.name not in plans:
                 plans[p.name] = p
         return list(plans.values())
@@ -146,11 +155,18 @@ class CausalLM:
         """Run the step described by ``ctx``; float32 logits [len(want), vocab] or None if nothing is wanted."""
         x = self.embedding.forward(ctx.token_ids, ctx.positions, self.position)
         stream = ResidualStream(x, self.dtype)
+        if self._keeps_embedding:
+            # a copy in the activation type: the layers change x in place
+            stream.x0 = stream.materialise()
+            stream.act = None
         nvtx = getattr(ctx, "nvtx", False)
         for i, st in enumerate(self.layer_order):
             if nvtx:
                 torch.cuda.nvtx.range_push(f"layer {i} (block {st.block})")
-            self.blocks[st.block].forward(stream, ctx, caches[st.cache].view(st.writes_cache))
+            stream.turn = st.turn
+            self.blocks[st.block].forward(stream, ctx, caches[st.cache].view(st.writes_cache) if st.cache >= 0 else None)
+            if self.after_layer is not None:
+                self.after_layer(i, stream)
             if nvtx:
                 torch.cuda.nvtx.range_pop()
         if ctx.n_want == 0:

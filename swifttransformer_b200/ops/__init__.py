@@ -856,6 +856,164 @@ def hgrn2_scan(proj: torch.Tensor, q_off: int, f_off: int, v_off: int, f_bias: t
     return out
 
 
+# ------------------------------------------------------------ latent attention
+def _latent_pool(pool: torch.Tensor, layer: int, kr: int, rot: int, page_size: int):
+    """(page stride, offset of the entry) in elements, for a pool [pages, entries, page_size * (kr + rot)]."""
+    assert pool.dim() == 3 and pool.is_contiguous() and pool.shape[2] == page_size * (kr + rot)
+    return ctypes.c_longlong(pool.stride(0)), ctypes.c_longlong(layer * pool.stride(1))
+
+
+def latent_prepare(proj: torch.Tensor, q_rank: int, q_norm: torch.Tensor, kv_norm: torch.Tensor, eps: float,
+                   inv_freq: torch.Tensor, rot_dims: int, cq: torch.Tensor, pool: torch.Tensor, layer: int,
+                   positions: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor,
+                   kr: int, rot: int, page_size: int, status: torch.Tensor, write_kv: bool = True) -> None:
+    """From the fused projection [query latent (q_rank) | key/value latent (kr) | shared key part (rot) | ...] of the
+    step's tokens: cq = the query latent, RMS-normed with ``q_norm``; the key/value latent RMS-normed with ``kv_norm``
+    and the shared key part, its first ``rot_dims`` dimensions rotated in halves by position * inv_freq, go to the
+    token's row of its page.  Statistics and angles are float."""
+    assert proj.is_contiguous() and proj.shape[1] >= q_rank + kr + rot and cq.shape == (proj.shape[0], q_rank)
+    assert cq.is_contiguous() and pool.dtype == proj.dtype == cq.dtype
+    stride, offset = _latent_pool(pool, layer, kr, rot, page_size)
+    _check(lib().st_latent_prepare(_p(proj), proj.shape[1], q_rank, _p(q_norm), _p(kv_norm), _f(eps), _p(inv_freq),
+                                   rot_dims, _p(cq), _p(pool), stride, offset, _p(positions), _p(seq_of_token),
+                                   _p(slots), _p(block_table), block_table.shape[1], proj.shape[0], kr, rot, page_size,
+                                   int(write_kv), _p(status), _dt(proj), _stream()), "latent_prepare")
+
+
+def latent_q_rotate(q: torch.Tensor, q_lat: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                    rot_dims: int, nh: int, dim: int, rot: int, kr: int) -> None:
+    """q [tokens, nh * (dim + rot)] -> the last ``rot`` numbers of every head's row of q_lat [tokens, nh, kr + rot]:
+    the head's rotated query part, turned by position."""
+    assert q.is_contiguous() and q_lat.is_contiguous() and q.dtype == q_lat.dtype
+    assert q.shape[1] == nh * (dim + rot) and q_lat.shape == (q.shape[0], nh * (kr + rot))
+    _check(lib().st_latent_q_rotate(_p(q), _p(q_lat), _p(positions), _p(inv_freq), rot_dims, q.shape[0], nh, dim, rot,
+                                    kr, _dt(q), _stream()), "latent_q_rotate")
+
+
+def latent_attention_plain(q_lat: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor,
+                           positions: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor,
+                           block_table: torch.Tensor, nh: int, kr: int, rot: int, page_size: int, scale: float,
+                           sink: Optional[torch.Tensor] = None, gates: Optional[torch.Tensor] = None,
+                           status: Optional[torch.Tensor] = None, items: Optional[torch.Tensor] = None,
+                           n_items: int = 0) -> torch.Tensor:
+    """Causal attention in the latent space, one block per (token, head), float arithmetic for either type:
+    out [tokens, nh * kr] = gate * softmax-with-sink(scale * q_lat . [c | k_rot]) c.  ``gates``: a view
+    [tokens, nh] (any row stride) of the heads' gate logits; ``sink`` float [nh]."""
+    assert q_lat.is_contiguous() and out.is_contiguous() and out.shape == (q_lat.shape[0], nh * kr)
+    stride, offset = _latent_pool(pool, layer, kr, rot, page_size)
+    if gates is not None:
+        assert gates.dtype == q_lat.dtype and gates.stride(1) == 1 and gates.shape == (q_lat.shape[0], nh)
+    _check(lib().st_latent_attention_plain(_p(q_lat), _p(pool), stride, offset, _p(out), _p(items), _p(positions),
+                                           _p(seq_of_token), _p(slots), _p(block_table), block_table.shape[1],
+                                           n_items if items is not None else q_lat.shape[0], nh, kr, rot, page_size,
+                                           _p(sink), _p(gates), gates.stride(0) if gates is not None else 0,
+                                           _f(scale), _p(status), _dt(q_lat), _stream()), "latent_attention_plain")
+    return out
+
+
+# ------------------------------------------------------------ grouped products, mixtures of experts
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_groups: int, k_dim: int, n_out: int,
+               a_goff: int, c_goff: int) -> torch.Tensor:
+    """out[:, g * c_goff + n] = sum_k a[:, g * a_goff + k] * w[g, n, k] for every group g: one product per head, each
+    on its own columns of ``a`` [rows, lda] and of ``out`` [rows, ldc]; w [groups, n_out, k_dim]."""
+    assert a.dim() == 2 and out.dim() == 2 and a.shape[0] == out.shape[0] and a.stride(1) == 1 and out.stride(1) == 1
+    assert w.is_contiguous() and w.shape == (n_groups, n_out, k_dim) and a.dtype == w.dtype
+    ll = ctypes.c_longlong
+    _check(lib().st_gemm_grouped_plain(_p(a), _p(w), _p(out), n_groups, a.shape[0], n_out, k_dim, 0, 0, ll(a.stride(0)),
+                                       ll(a_goff), ll(out.stride(0)), ll(c_goff), ll(n_out * k_dim), None, None, None, 0,
+                                       None, 1, _dt(a), int(out.dtype == torch.float32), _stream()), "gemm_heads")
+    return out
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, positions: Optional[torch.Tensor] = None,
+              w_gate: Optional[torch.Tensor] = None, renorm: bool = False):
+    """-> (experts int32 [tokens, top], weights float [tokens, top], gate float [tokens] or None).  Router logits,
+    softmax over all experts and the choice in float; ``w_router`` float [experts, width]; ``w_gate`` float [width]:
+    also sigmoid(w_gate . h) per token.  Tokens at a negative position get expert -1."""
+    n, width = h.shape
+    assert h.is_contiguous() and w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == width
+    experts = torch.empty((n, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    gate = torch.empty((n,), dtype=torch.float32, device=h.device) if w_gate is not None else None
+    if w_gate is not None:
+        assert w_gate.dtype == torch.float32 and w_gate.numel() == width and w_gate.is_contiguous()
+    _check(lib().st_moe_route(_p(h), n, width, _p(w_router), w_router.shape[0], top, int(renorm), _p(w_gate),
+                              _p(positions), _p(experts), _p(weights), _p(gate), _dt(h), _stream()), "moe_route")
+    return experts, weights, gate
+
+
+def grouped_tile_rows() -> int:
+    return int(lib().st_gemm_grouped_tile_rows())
+
+
+class ExpertOrder:
+    """The step's (token, choice) items grouped by expert (device arrays, see ``moe_sort``)."""
+
+    def __init__(self, offsets, sorted_items, place, tile_group, tile_row0, n_items, top):
+        self.offsets, self.sorted, self.place = offsets, sorted_items, place
+        self.tile_group, self.tile_row0, self.n_items, self.top = tile_group, tile_row0, n_items, top
+
+
+def moe_sort(experts: torch.Tensor, n_experts: int) -> ExpertOrder:
+    """Group the (token, choice) items of ``experts`` [tokens, top] by expert; everything stays on the device."""
+    n, top = experts.shape
+    items, rows = n * top, grouped_tile_rows()
+    cap = (items + rows - 1) // rows + n_experts
+    buf = torch.empty(n_experts + 1 + 2 * items + 2 * cap, dtype=torch.int32, device=experts.device)
+    offsets, rest = buf[:n_experts + 1], buf[n_experts + 1:]
+    sorted_items, place, tile_group, tile_row0 = rest[:items], rest[items:2 * items], rest[2 * items:2 * items + cap], rest[2 * items + cap:]
+    _check(lib().st_moe_sort(_p(experts), items, n_experts, rows, cap, _p(offsets), _p(sorted_items), _p(place),
+                             _p(tile_group), _p(tile_row0), _stream()), "moe_sort")
+    return ExpertOrder(offsets, sorted_items, place, tile_group, tile_row0, items, top)
+
+
+def gemm_experts(a: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gather: bool, gated: bool = False,
+                 act: str = "none") -> torch.Tensor:
+    """One product per expert over the rows the order gives it: out [items, n_out] in sorted order.
+    ``gather``: the rows of ``a`` are the tokens (row of item i = i // top), else ``a`` is already in sorted order.
+    w [experts, n_out (twice with ``gated``: gate rows, then up rows), k]; gated: out = act(gate) * up."""
+    assert a.is_contiguous() and w.is_contiguous() and w.dim() == 3 and a.dtype == w.dtype and a.shape[1] == w.shape[2]
+    n_out = w.shape[1] // 2 if gated else w.shape[1]
+    out = torch.empty((order.n_items, n_out), dtype=a.dtype, device=a.device)
+    ll = ctypes.c_longlong
+    _check(lib().st_gemm_grouped_plain(_p(a), _p(w), _p(out), w.shape[0], order.n_items, n_out, w.shape[2], int(gated),
+                                       ACT_CODES[act], ll(a.stride(0)), ll(0), ll(n_out), ll(0),
+                                       ll(w.shape[1] * w.shape[2]), _p(order.offsets), _p(order.tile_group),
+                                       _p(order.tile_row0), order.tile_group.numel(),
+                                       _p(order.sorted) if gather else None, order.top if gather else 1, _dt(a), 0,
+                                       _stream()), "gemm_experts")
+    return out
+
+
+def moe_combine(y: torch.Tensor, order: ExpertOrder, weights: torch.Tensor, shared: Optional[torch.Tensor] = None,
+                gate: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * y[place of (t, k)] (+ gate[t] * shared[t]); sums in float."""
+    n, top = weights.shape
+    width = y.shape[1]
+    assert y.is_contiguous() and (shared is None or (shared.is_contiguous() and shared.dtype == y.dtype and gate is not None))
+    out = torch.empty((n, width), dtype=out_dtype, device=y.device)
+    _check(lib().st_moe_combine(_p(y), _p(order.place), _p(weights), top, _p(shared), _p(gate), n, width, _p(out),
+                                _dt(y), int(out_dtype == torch.float32), _stream()), "moe_combine")
+    return out
+
+
+def concat_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """[a | b] row by row in b's type; ``a`` may be float32 (the residual rows)."""
+    assert a.is_contiguous() and b.is_contiguous() and a.shape[0] == b.shape[0]
+    assert a.dtype == b.dtype or a.dtype == torch.float32
+    out = torch.empty((a.shape[0], a.shape[1] + b.shape[1]), dtype=b.dtype, device=b.device)
+    _check(lib().st_concat_rows(_p(a), int(a.dtype == torch.float32), a.shape[1], _p(b), b.shape[1], _p(out), a.shape[0],
+                                _dt(b), _stream()), "concat_rows")
+    return out
+
+
+def scale_softcap(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """x <- cap * tanh(x * scale / cap) in place on float32 values (cap <= 0: x <- x * scale)."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(lib().st_scale_softcap(_p(x), ctypes.c_longlong(x.numel()), _f(scale), _f(cap), _stream()), "scale_softcap")
+    return x
+
+
 # ------------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Lowest index of the largest value of each row of float32 logits -> int32 [rows]."""

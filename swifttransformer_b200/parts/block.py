@@ -7,6 +7,10 @@ post_norm (do_layer_norm_before false; the reference refuses it, gpt.cc:238-240)
     r = norm1(x + mixer(x));  x' = norm2(r + ffn(r))
 norm_after (the norm on the sub-layer's output only; the sub-layers read x itself):
     r = x + mult * norm1(mixer(x));  x' = r + mult * norm2(ffn(r))
+parallel  (one norm, both sub-layers read its output):
+    h = norm1(x);  x' = x + (mixer(h) + ffn(h))
+reentry   (no sub-layers; opens a pass over a stretch of layers that runs several times):
+    x' = W [x ; x0] + step[turn]         x0: the embedding's rows, turn: the number of the pass
 
 The residual stream is float32 for every storage type.  A block leaves the
 feed-forward's result as ``pending``: the next norm kernel (of the next block
@@ -30,6 +34,8 @@ class ResidualStream:
     act_dtype: torch.dtype
     pending: Optional[Delta] = None        # still to be added to x
     act: Optional[torch.Tensor] = None     # x in the activation dtype, when current
+    x0: Optional[torch.Tensor] = None      # the embedding's rows in the activation dtype (models that ask for them)
+    turn: int = 0                          # which pass over a stretch of shared layers the running step belongs to
 
     def materialise(self, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x + pending in the activation dtype (all rows, folding pending into x; or only ``rows``)."""
@@ -134,3 +140,73 @@ class NormAfterBlock(Block):
             assert f.bias is None and f.parts is None
             ops.norm_add(x, f.value, self.norm2.gain, self.mult, self.norm2.eps, ctx.positions)
         stream.pending = None
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    """h = norm1(x); x <- x + (mixer(h) + ffn(h)): one norm, and both sub-layers read its output.  The feed-forward
+    may be absent.  The mixer's result (activation type) and the feed-forward's (float, when it can leave it so) are
+    left pending together: the next norm kernel forms their sum and adds it to the float residual rows."""
+
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], norm1: Norm):
+        super().__init__(mixer, feed_forward, norm1, None)
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.norm1, self.mixer, self.feed_forward) if p is not None]
+
+    def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
+        h = self.norm1.apply(stream.x, stream.pending, act_dtype=stream.act_dtype)
+        a = self.mixer.forward(h, ctx, cache)
+        assert a.bias is None and a.parts is None
+        pending = a
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(h, ctx)
+            assert f.bias is None
+            if f.parts is not None:
+                assert f.value is None
+                pending = Delta(a.value, None, f.parts)
+            elif f.value.dtype == torch.float32 and f.value.is_contiguous():
+                pending = Delta(a.value, None, f.value.unsqueeze(0))
+            else:
+                # the feed-forward's result in the activation type: one more pass adds the mixer's to the residual
+                # rows first (the two are not summed in the activation type)
+                ops.add_norm(stream.x, delta=a.value, resid_out=stream.x, kind="none", act_dtype=stream.act_dtype)
+                pending = f
+        stream.pending, stream.act = pending, None
+
+
+@BLOCKS.register("reentry")
+class ReentryBlock(Block):
+    """Opens a pass over a stretch of layers that runs several times with the same weights:
+    x <- W [x ; x0] + step[turn], with x0 the embedding's rows (``ResidualStream.x0``), W [width, 2 * width] (x's
+    columns first) and step [passes, width]; ``ResidualStream.turn`` says which pass begins.  The product's float
+    result becomes the residual stream; the step vector is left pending for the next norm kernel.  It has no mixer,
+    no cache and no norm."""
+
+    wants_embedding = True
+
+    def __init__(self, width: int, passes: int, in_name: str, step_name: str):
+        super().__init__(None, None, None, None)
+        self.width, self.passes, self.in_name, self.step_name = width, passes, in_name, step_name
+        self.w_in = self.step = None
+
+    def children(self) -> List[Part]:
+        return []
+
+    def param_specs(self):
+        from ..weights.spec import MATRIX, VECTOR, ParamSpec
+        return [ParamSpec(self.in_name, (self.width, 2 * self.width), MATRIX),
+                ParamSpec(self.step_name, (self.passes, self.width), VECTOR)]
+
+    def bind(self, tensors) -> None:
+        self.w_in, self.step = tensors[self.in_name], tensors[self.step_name]
+
+    def param_bytes(self) -> int:
+        return self.w_in.numel() * self.w_in.element_size() + 4 * self.width
+
+    def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
+        if stream.x0 is None:
+            raise RuntimeError("a reentry block needs the embedding's rows (ResidualStream.x0)")
+        both = ops.concat_rows(stream.materialise(), stream.x0)
+        stream.x = ops.linear(both, self.w_in, out_dtype=torch.float32)
+        stream.pending, stream.act = Delta(None, self.step[stream.turn]), None

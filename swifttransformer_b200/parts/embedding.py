@@ -67,11 +67,14 @@ class Embedding(Part):
 
 
 class OutputHead(Part):
-    """logits = (project_out . h) . table^T as float32."""
+    """logits = (project_out . h) . table^T as float32; with ``scale`` and ``softcap`` (0: none),
+    logits <- softcap * tanh(logits * scale / softcap)."""
 
     def __init__(self, vocab: int, embed_width: int, hidden: int, weight_name: str,
-                 tied_to: Optional[str] = None, project_out_name: Optional[str] = None):
+                 tied_to: Optional[str] = None, project_out_name: Optional[str] = None, scale: float = 1.0,
+                 softcap: float = 0.0):
         self.vocab, self.embed_width, self.hidden = vocab, embed_width, hidden
+        self.scale, self.softcap = float(scale), float(softcap or 0.0)
         self.weight_name, self.tied_to, self.project_out_name = weight_name, tied_to, project_out_name
         self.weight: Optional[torch.Tensor] = None
         self.project_out: Optional[torch.Tensor] = None
@@ -90,7 +93,10 @@ class OutputHead(Part):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         if self.project_out is not None:
             h = ops.linear(h, self.project_out)
-        return ops.linear(h, self.weight, out_dtype=torch.float32)
+        logits = ops.linear(h, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0 or self.softcap > 0.0:
+            ops.scale_softcap(logits, self.scale, self.softcap)
+        return logits
 
     def param_bytes(self) -> int:
         b = self.weight.numel() * self.weight.element_size()

@@ -70,9 +70,12 @@ class DenseFFN(FeedForward):
 @FEED_FORWARDS.register("gated")
 class GatedFFN(FeedForward):
     """z = down(act(gate h) * (up h)), no biases.  The gate and up matrices are stacked at load time so that one
-    product gives both; ``activation`` is any of ops.ACT_CODES (the tanh form of GELU, SiLU, ...)."""
+    product gives both; ``activation`` is any of ops.ACT_CODES (the tanh form of GELU, SiLU, ...).  ``float_out``:
+    the down product leaves its float sums as they are (a block that adds two sub-layers' results takes them so)."""
 
-    def __init__(self, hidden: int, inner: int, activation: str, gate_name: str, up_name: str, down_name: str):
+    def __init__(self, hidden: int, inner: int, activation: str, gate_name: str, up_name: str, down_name: str,
+                 float_out: bool = False):
+        self.float_out = float_out
         if activation not in ops.ACT_CODES:
             raise ValueError(f"activation '{activation}' is not supported ({', '.join(ops.ACT_CODES)})")
         self.hidden, self.inner, self.activation = hidden, inner, activation
@@ -90,7 +93,7 @@ class GatedFFN(FeedForward):
 
     def forward(self, h: torch.Tensor, ctx: Any) -> Delta:
         u = ops.gated_act(ops.linear(h, self.w_gu), self.activation)
-        return Delta(ops.linear(u, self.w_down))
+        return Delta(ops.linear(u, self.w_down, out_dtype=torch.float32 if self.float_out else None))
 
     def param_bytes(self) -> int:
         return (self.w_gu.numel() + self.w_down.numel()) * self.w_gu.element_size()

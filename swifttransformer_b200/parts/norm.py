@@ -106,6 +106,27 @@ class ScalarRMSNorm(Norm):
         return 4
 
 
+@NORMS.register("rmsnorm_offset")
+class OffsetRMSNorm(Norm):
+    """RMS norm whose weight is kept as its difference from one: y = x / sqrt(mean(x^2) + eps) * (1 + w).  The tensor ``name``
+    holds w; 1 + w is formed once, in float, when the weights are bound, and the kernel of the other norms does the
+    rest."""
+    kind = "rmsnorm"
+
+    def __init__(self, width: int, eps: float = 1e-5, affine: bool = True, prefix: str = "", name: str = ""):
+        super().__init__(width, eps, affine, prefix)
+        self.name = name or prefix
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec(self.name, (self.width,), VECTOR)]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.gamma = (tensors[self.name].to(torch.float32) + 1.0).contiguous()
+
+    def param_bytes(self) -> int:
+        return 4 * self.width
+
+
 @NORMS.register("none")
 class NoNorm(Norm):
     """Residual add and cast only."""

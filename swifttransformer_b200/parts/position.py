@@ -82,3 +82,10 @@ class RotaryPairs(PositionEncoding):
             f = [math.pow(self.base, -2.0 * i / self.dims) for i in range(self.dims // 2)] or [0.0]
             self._tables[device] = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
         return self._tables[device]
+
+
+@POSITION_ENCODINGS.register("rotary_halves")
+class RotaryHalves(RotaryPairs):
+    """The same rotation with the other pairing: of the first ``dims`` dimensions of a vector, dimension i is paired
+    with dimension i + dims/2 (the two halves, not neighbours), i = 0 .. dims/2 - 1, at the angle
+    p * base^(-2i/dims).  A mixer that rotates in a kernel of its own takes ``inv_freq`` and ``dims`` from here."""
