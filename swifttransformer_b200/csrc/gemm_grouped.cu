@@ -10,9 +10,13 @@
 //     given (the sorted (token, choice) items, a_row_div choices per token), else the row itself.
 // Epilogue: none, or "gated": w[g] holds 2 * n_out rows, gate rows first, and c = act(gate) * up.
 //
+// gemm_grouped_mma: bfloat16 on the warp-level tensor cores (mma.sync m16n8k16, float accumulation): tiles of 64 rows
+// x 64 outputs x 32 of k, four warps of 32 x 32 each, rows gathered and weights streamed by 16-byte asynchronous
+// copies in two stages; k, the row strides and the group offsets must be multiples of 8 elements.
 // gemm_grouped_plain: float arithmetic for either storage type; every output element is one chain of fused
 // multiply-adds over k in ascending order whatever rows share its tile (the 32-bit path, and the plain twin).
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 struct GroupedShape {
     int n_rows, n_out, k_dim, gated, act;
@@ -136,6 +140,154 @@ ST_EXPORT int st_gemm_grouped_plain(const void* a, const void* w, void* c, int n
         return st_launch_pdl("gemm_grouped", gemm_grouped_plain_kernel<bf16, float>, grid, dim3(256), 0, s, (const bf16*)a,
                              (const bf16*)w, (float*)c, sh);
     return st_launch_pdl("gemm_grouped", gemm_grouped_plain_kernel<bf16, bf16>, grid, dim3(256), 0, s, (const bf16*)a,
+                         (const bf16*)w, (bf16*)c, sh);
+}
+
+#define GM_BK 32
+#define GM_LD (GM_BK + 8)
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(128)
+gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TO* __restrict__ c, GroupedShape sh) {
+    __shared__ __align__(16) bf16 sa[2][GG_BM][GM_LD];
+    __shared__ __align__(16) bf16 sw[2][GATED ? 2 * GG_BN : GG_BN][GM_LD];
+    __shared__ int srow[GG_BM];
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    int g, row0, row_end;
+    if (sh.offsets) {
+        g = __ldcg(sh.tile_group + blockIdx.y);
+        if (g < 0) return;
+        row0 = __ldcg(sh.tile_row0 + blockIdx.y);
+        row_end = min(row0 + GG_BM, __ldcg(sh.offsets + g + 1));
+    } else {
+        g = blockIdx.z;
+        row0 = blockIdx.y * GG_BM;
+        row_end = min(row0 + GG_BM, sh.n_rows);
+    }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < GG_BM) {
+        const int r = row0 + tid;
+        int ar = -1;
+        if (r < row_end) ar = sh.a_rows ? __ldcg(sh.a_rows + r) / sh.a_row_div : r;
+        srow[tid] = ar;
+    }
+    __syncthreads();
+    const int col0 = blockIdx.x * GG_BN;
+    const bf16* wg = w + (long long)g * sh.w_gstride;
+    const bf16* ag = a + g * sh.a_goff;
+    auto load = [&](int k0, int stage) {
+        // 64 rows x 4 chunks of 8 per operand
+        for (int ch = tid; ch < GG_BM * 4; ch += 128) {
+            const int r = ch >> 2, kc = (ch & 3) * 8;
+            const int ar = srow[r];
+            const bool ok = ar >= 0 && k0 + kc < sh.k_dim;
+            cp_async16(&sa[stage][r][kc], ok ? ag + (long long)ar * sh.lda + k0 + kc : a, ok);
+        }
+        for (int ch = tid; ch < GG_BN * 4 * (GATED ? 2 : 1); ch += 128) {
+            const int r = ch >> 2, kc = (ch & 3) * 8;
+            const int n = col0 + (r & (GG_BN - 1)) + (r >= GG_BN ? sh.n_out : 0);
+            const bool ok = col0 + (r & (GG_BN - 1)) < sh.n_out && k0 + kc < sh.k_dim;
+            cp_async16(&sw[stage][r][kc], ok ? wg + (long long)n * sh.k_dim + k0 + kc : w, ok);
+        }
+    };
+    float acc[2][4][4], acu[GATED ? 2 : 1][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[i][j][e] = 0.f;
+                if (GATED) acu[i][j][e] = 0.f;
+            }
+    const int wm = (warp & 1) * 32, wn = (warp >> 1) * 32;
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+    const int n_k = (sh.k_dim + GM_BK - 1) / GM_BK;
+    load(0, 0);
+    cp_async_commit();
+    for (int kt = 0; kt < n_k; ++kt) {
+        const int stage = kt & 1;
+        if (kt + 1 < n_k) {
+            load((kt + 1) * GM_BK, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GM_BK; kk += 16) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(af[i][0], af[i][1], af[i][2], af[i][3], &sa[stage][wm + i * 16 + a_row][kk + a_col]);
+#pragma unroll
+            for (int jp = 0; jp < 2; ++jp) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, &sw[stage][wn + jp * 16 + b_row][kk + b_col]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma_bf16(acc[i][2 * jp], af[i], b0, b1);
+                    mma_bf16(acc[i][2 * jp + 1], af[i], b2, b3);
+                }
+                if (GATED) {
+                    ldmatrix_x4(b0, b1, b2, b3, &sw[stage][GG_BN + wn + jp * 16 + b_row][kk + b_col]);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        mma_bf16(acu[i][2 * jp], af[i], b0, b1);
+                        mma_bf16(acu[i][2 * jp + 1], af[i], b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = row0 + wm + i * 16 + gq + (e >> 1) * 8;
+                const int n = col0 + wn + j * 8 + 2 * tq + (e & 1);
+                if (r >= row_end || n >= sh.n_out) continue;
+                float v = acc[i][j][e];
+                if (GATED) v = apply_act(to_f32(from_f32<bf16>(v)), sh.act) * to_f32(from_f32<bf16>(acu[i][j][e]));
+                c[(long long)r * sh.ldc + g * sh.c_goff + n] = from_f32<TO>(v);
+            }
+}
+
+ST_EXPORT int st_gemm_grouped_mma_applies(int k_dim, long long lda, long long a_goff, long long w_gstride) {
+    return k_dim > 0 && k_dim % 8 == 0 && lda % 8 == 0 && a_goff % 8 == 0 && w_gstride % 8 == 0;
+}
+
+ST_EXPORT int st_gemm_grouped_mma(const void* a, const void* w, void* c, int n_groups, int n_rows, int n_out, int k_dim,
+                                  int gated, int act, long long lda, long long a_goff, long long ldc, long long c_goff,
+                                  long long w_gstride, const int* offsets, const int* tile_group, const int* tile_row0,
+                                  int n_tiles, const int* a_rows, int a_row_div, int out_f32, void* stream) {
+    if (n_groups <= 0 || n_out <= 0) return 0;
+    if ((offsets && (!tile_group || !tile_row0 || n_tiles <= 0)) || (a_rows && a_row_div <= 0)) return ST_ERR_BAD_ARG;
+    if (!offsets && n_rows <= 0) return 0;
+    if (!st_gemm_grouped_mma_applies(k_dim, lda, a_goff, w_gstride) || !aligned16(a) || !aligned16(w)) return ST_ERR_BAD_SIZE;
+    GroupedShape sh{n_rows, n_out, k_dim, gated, act, lda, a_goff, ldc, c_goff, w_gstride, offsets, tile_group, tile_row0,
+                    a_rows, a_row_div};
+    dim3 grid((n_out + GG_BN - 1) / GG_BN, offsets ? n_tiles : (n_rows + GG_BM - 1) / GG_BM, offsets ? 1 : n_groups);
+    if (grid.y > 65535 || grid.z > 65535) return ST_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (gated) {
+        if (out_f32)
+            return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<float, true>, grid, dim3(128), 0, s, (const bf16*)a,
+                                 (const bf16*)w, (float*)c, sh);
+        return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<bf16, true>, grid, dim3(128), 0, s, (const bf16*)a,
+                             (const bf16*)w, (bf16*)c, sh);
+    }
+    if (out_f32)
+        return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<float, false>, grid, dim3(128), 0, s, (const bf16*)a,
+                             (const bf16*)w, (float*)c, sh);
+    return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<bf16, false>, grid, dim3(128), 0, s, (const bf16*)a,
                          (const bf16*)w, (bf16*)c, sh);
 }
 

@@ -1,0 +1,283 @@
+// Latent attention on the warp-level tensor cores (bfloat16): the kernel for prompt portions and for single tokens.
+//
+// All heads read the same cached rows [c | k_rot], so the rows of the query tile are (token, head) pairs: 64
+// consecutive pairs of one request's tokens of the step, in the order the latent-space queries lie in memory
+// ([token][head][kr + rot]).  A single decoded token of a model with H heads is a tile of H rows; a prompt portion
+// of n tokens is ceil(n * H / 64) tiles, and every row carries its own causal limit (its token's position).
+//
+// Per tile of 32 keys (aligned to absolute positions, so a row's sums do not depend on how the request was cut):
+//   S = Q K^T        eight warps: four groups of 16 rows x two halves of 16 keys, mma.sync m16n8k16 over kr + rot
+//   softmax          float, running maximum and sums per row (the halves meet through shared memory)
+//   O += P V         V is the first kr numbers of the very rows that were the keys: the warp of (row group, half)
+//                    owns 16 rows x half of the value columns; P goes through shared memory as bfloat16
+// and at the end the sink joins the denominator, the gate multiplies, and the row is stored.
+// The key tiles arrive by 16-byte asynchronous copies, two stages.  NT: value columns per warp / 8 (the block covers
+// NT * 16 >= kr columns; the template keeps the accumulator in registers).
+#include "latent_attention.cuh"
+#include "mma_sync.cuh"
+
+#define LM_ROWS 64
+#define LM_KEYS 32
+#define LM_THREADS 256
+#define LM_PLD 40          // row stride of the P tile in elements
+
+template <int NT>
+__global__ void __launch_bounds__(LM_THREADS, 1)
+latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restrict__ pool, LatentCache cache,
+                            bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ q_start,
+                            const int* __restrict__ start_pos, const int* __restrict__ slots,
+                            const int* __restrict__ block_table, int n_seqs, const float* __restrict__ sink,
+                            const bf16* __restrict__ gates, int gate_ld, int nh, float scale_log2, int lds, int kdp,
+                            int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                 // [64][lds]
+    bf16* sK = sQ + LM_ROWS * lds;                                // [2][32][lds]
+    bf16* sP = sK + 2 * LM_KEYS * lds;                            // [64][LM_PLD]
+    float* smax = reinterpret_cast<float*>(sP + LM_ROWS * LM_PLD);  // [2][64]
+    float* ssum = smax + 2 * LM_ROWS;                             // [2][64]
+    __shared__ int s_req, s_tile;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, rg = warp & 3, half = warp >> 2;
+    const int g = lane >> 2, tq = lane & 3;
+    const int kr = cache.kr, kd = cache.kr + cache.rot, ps = cache.page_size;
+
+    // zero the tiles once: the columns between kd and the padded width are read by the products
+    for (int i = tid * 8; i < (LM_ROWS + 2 * LM_KEYS) * lds; i += LM_THREADS * 8)
+        *reinterpret_cast<uint4*>(sQ + i) = make_uint4(0, 0, 0, 0);
+    if (tid == 0) {
+        int tile = blockIdx.x, req = -1;
+        for (int i = 0; i < n_seqs; ++i) {
+            const int rows = (q_start[i + 1] - q_start[i]) * nh;
+            const int tiles = (rows + LM_ROWS - 1) / LM_ROWS;
+            if (tile < tiles) { req = i; break; }
+            tile -= tiles;
+        }
+        s_req = req;
+        s_tile = tile;
+    }
+    ST_PDL_WAIT();
+    ST_PDL_TRIGGER();
+    __syncthreads();
+    const int b = s_req;
+    if (b < 0) return;
+    const int tok0 = q_start[b], n_rows = (q_start[b + 1] - tok0) * nh, r0 = s_tile * LM_ROWS;
+    if (positions[tok0] < 0) return;                    // a padding request of a fixed-shape step
+    const int start = start_pos[b];
+    const int* bt = block_table + (size_t)slots[b] * cache.max_pages;
+    const int last_row = min(r0 + LM_ROWS, n_rows) - 1;
+    const int hi = start + last_row / nh + 1;           // keys 0 .. hi-1 are seen by some row of the tile
+    const int chunks = kd / 8;
+
+    // the queries: the tile's rows are consecutive in memory
+    {
+        const bf16* src = q_lat + ((size_t)tok0 * nh + r0) * kd;
+        const int rows_here = last_row - r0 + 1;
+        for (int c = tid; c < LM_ROWS * chunks; c += LM_THREADS) {
+            const int r = c / chunks, ch = c - r * chunks;
+            cp_async16(sQ + r * lds + ch * 8, src + (size_t)r * kd + ch * 8, r < rows_here);
+        }
+    }
+    auto load_keys = [&](int kt, int stage) {
+        bf16* dst = sK + stage * LM_KEYS * lds;
+        for (int c = tid; c < LM_KEYS * chunks; c += LM_THREADS) {
+            const int key = c / chunks, ch = c - key * chunks;
+            const int j = kt * LM_KEYS + key;
+            bool ok = j < hi;
+            const bf16* src = pool;
+            if (ok) {
+                const int page = bt[j / ps];
+                if (page >= 0) src = latent_row(pool, cache, page, j % ps) + ch * 8;
+                else { ok = false; if (status) *status = 1; }
+            }
+            cp_async16(dst + key * lds + ch * 8, src, ok);
+        }
+    };
+    const int n_kt = (hi + LM_KEYS - 1) / LM_KEYS;
+    load_keys(0, 0);
+    cp_async_commit();
+
+    const int row_a = rg * 16 + g, row_b = row_a + 8;
+    const int pos_a = r0 + row_a <= last_row ? start + (r0 + row_a) / nh : -1;
+    const int pos_b = r0 + row_b <= last_row ? start + (r0 + row_b) / nh : -1;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    // lane-dependent parts of the ldmatrix addresses
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;      // A operands, and V (transposed)
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;      // K as the B operand
+
+    for (int kt = 0; kt < n_kt; ++kt) {
+        const int stage = kt & 1;
+        if (kt + 1 < n_kt) {
+            load_keys(kt + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const bf16* kb = sK + stage * LM_KEYS * lds;
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            const uint32_t qa = smem_u32(sQ + (rg * 16 + a_row) * lds + a_col);
+            const uint32_t ka = smem_u32(kb + (half * 16 + b_row) * lds + b_col);
+            for (int k0 = 0; k0 < kdp; k0 += 16) {
+                uint32_t a[4], b0, b1, b2, b3;
+                ldmatrix_x4_s(a[0], a[1], a[2], a[3], qa + k0 * 2);
+                ldmatrix_x4_s(b0, b1, b2, b3, ka + k0 * 2);
+                mma_bf16(s[0], a, b0, b1);
+                mma_bf16(s[1], a, b2, b3);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kt * LM_KEYS + half * 16 + nt * 8 + 2 * tq + (e & 1);
+                const int limit = e < 2 ? pos_a : pos_b;
+                const float v = j <= limit ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        }
+        if (tq == 0) {
+            smax[half * LM_ROWS + row_a] = mx[0];
+            smax[half * LM_ROWS + row_b] = mx[1];
+        }
+        __syncthreads();
+        float corr[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = i ? row_b : row_a;
+            const float mn = fmaxf(m[i], fmaxf(smax[row], smax[LM_ROWS + row]));
+            corr[i] = m[i] == -INFINITY ? 0.f : fast_exp2(m[i] - mn);
+            m[i] = mn;
+        }
+        float add[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = s[nt][e] == -INFINITY ? 0.f : fast_exp2(s[nt][e] - m[e >> 1]);
+                add[e >> 1] += p[e];
+            }
+            const int col = half * 16 + nt * 8 + 2 * tq;
+            *reinterpret_cast<uint32_t*>(sP + row_a * LM_PLD + col) = pack_bf16(p[0], p[1]);
+            *reinterpret_cast<uint32_t*>(sP + row_b * LM_PLD + col) = pack_bf16(p[2], p[3]);
+        }
+        l[0] = l[0] * corr[0] + add[0];
+        l[1] = l[1] * corr[1] + add[1];
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            uint32_t a[4];
+            ldmatrix_x4(a[0], a[1], a[2], a[3], sP + (rg * 16 + a_row) * LM_PLD + kk * 16 + a_col);
+            const uint32_t va = smem_u32(kb + (kk * 16 + a_row) * lds + half * NT * 8 + a_col);
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans_s(b0, b1, b2, b3, va + np * 32);
+                mma_bf16(o[2 * np], a, b0, b1);
+                mma_bf16(o[2 * np + 1], a, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+    // the halves' sums meet; the sink joins the denominator; the gate multiplies
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+    if (tq == 0) {
+        ssum[half * LM_ROWS + row_a] = l[0];
+        ssum[half * LM_ROWS + row_b] = l[1];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = i ? row_b : row_a;
+        if (r0 + row > last_row) continue;
+        const int tok = tok0 + (r0 + row) / nh, h = (r0 + row) % nh;
+        const float snk = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
+        const float mf = fmaxf(m[i], snk);
+        const float c = m[i] == -INFINITY ? 0.f : exp2f(m[i] - mf);
+        const float den = (ssum[row] + ssum[LM_ROWS + row]) * c + (snk > -INFINITY ? exp2f(snk - mf) : 0.f);
+        float gate = 1.f;
+        if (gates) gate = 1.f / (1.f + expf(-load1_cg(gates + (size_t)tok * gate_ld + h)));
+        const float k = den > 0.f ? c * gate / den : 0.f;
+        bf16* dst = out + ((size_t)tok * nh + h) * kr;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int col = half * NT * 8 + nt * 8 + 2 * tq;
+            if (col < kr)
+                *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(o[nt][2 * i] * k, o[nt][2 * i + 1] * k);
+        }
+    }
+}
+
+static int lm_row_stride(int kr, int rot, int nt) {
+    const int kdp = (kr + rot + 15) / 16 * 16;
+    return (kdp > nt * 16 ? kdp : nt * 16) + 8;
+}
+static size_t lm_smem(int lds) {
+    return (size_t)(LM_ROWS + 2 * LM_KEYS) * lds * sizeof(bf16) + LM_ROWS * LM_PLD * sizeof(bf16) + 4 * LM_ROWS * sizeof(float);
+}
+static int lm_nt(int kr) {
+    const int sizes[] = {2, 4, 6, 8, 12, 16, 24, 32};
+    for (int nt : sizes)
+        if (nt * 16 >= kr) return nt;
+    return 0;
+}
+
+// bfloat16; kr a multiple of 16 up to 512; kr + rot a multiple of 8; the tiles must fit the shared memory of an SM
+ST_EXPORT int st_latent_attention_mma_applies(int kr, int rot) {
+    const int nt = lm_nt(kr);
+    if (kr <= 0 || kr % 16 || rot < 0 || (kr + rot) % 8 || !nt) return 0;
+    return lm_smem(lm_row_stride(kr, rot, nt)) <= 200 * 1024;
+}
+
+ST_EXPORT int st_latent_attention_mma(const void* q_lat, const void* pool, long long page_stride, long long entry_offset,
+                                      void* out, const int* positions, const int* q_start, const int* start_pos,
+                                      const int* slots, const int* block_table, int max_pages, int n_tokens, int n_seqs,
+                                      int nh, int kr, int rot, int page_size, const float* sink, const void* gates,
+                                      int gate_ld, float scale, int* status, void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (!st_latent_attention_mma_applies(kr, rot) || page_stride % 8 || entry_offset % 8) return ST_ERR_BAD_SIZE;
+    if (!aligned16(q_lat) || !aligned16(pool)) return ST_ERR_BAD_ARG;
+    LatentCache c{max_pages, page_size, kr, rot, page_stride, entry_offset};
+    const int nt = lm_nt(kr), lds = lm_row_stride(kr, rot, nt), kdp = (kr + rot + 15) / 16 * 16;
+    const size_t smem = lm_smem(lds);
+    const long long tiles = ((long long)n_tokens * nh + LM_ROWS - 1) / LM_ROWS + n_seqs;
+    if (tiles > 0x7fffffff) return ST_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const float scale_log2 = scale * 1.4426950408889634f;
+#define LM_LAUNCH(NTV)                                                                                               \
+    case NTV: {                                                                                                      \
+        static bool set = false;                                                                                     \
+        if (!set) {                                                                                                  \
+            cudaFuncSetAttribute(latent_attention_mma_kernel<NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            set = true;                                                                                              \
+        }                                                                                                            \
+        return st_launch_pdl("latent_mma", latent_attention_mma_kernel<NTV>, dim3((unsigned)tiles), dim3(LM_THREADS), smem, s, \
+                             (const bf16*)q_lat, (const bf16*)pool, c, (bf16*)out, positions, q_start, start_pos, slots,    \
+                             block_table, n_seqs, sink, (const bf16*)gates, gate_ld, nh, scale_log2, lds, kdp, status);     \
+    }
+    switch (nt) {
+        LM_LAUNCH(2) LM_LAUNCH(4) LM_LAUNCH(6) LM_LAUNCH(8) LM_LAUNCH(12) LM_LAUNCH(16) LM_LAUNCH(24) LM_LAUNCH(32)
+    }
+#undef LM_LAUNCH
+    return ST_ERR_BAD_SIZE;
+}

@@ -911,6 +911,49 @@ def latent_attention_plain(q_lat: torch.Tensor, pool: torch.Tensor, layer: int, 
     return out
 
 
+def latent_attention_mma_applies(q_lat: torch.Tensor, kr: int, rot: int) -> bool:
+    """Whether the tensor-core kernel takes these sizes: bfloat16, kr a multiple of 16 up to 512, kr + rot a multiple
+    of 8, tiles that fit an SM's shared memory."""
+    return q_lat.is_cuda and q_lat.dtype == torch.bfloat16 and bool(lib().st_latent_attention_mma_applies(kr, rot))
+
+
+def latent_attention(q_lat: torch.Tensor, pool: torch.Tensor, layer: int, out: torch.Tensor, positions: torch.Tensor,
+                     seq_of_token: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, nh: int, kr: int,
+                     rot: int, page_size: int, scale: float, sink: Optional[torch.Tensor] = None,
+                     gates: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, kernel: str = "auto",
+                     q_start: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None, n_seqs: int = 0,
+                     lens=None, start=None) -> torch.Tensor:
+    """Latent attention of the step's queries (see ``latent_attention_plain`` for the arguments).  kernel: "mma" = the
+    tensor-core kernel over tiles of 64 (token, head) rows (bfloat16; it needs the step's requests: ``q_start``
+    [n_seqs + 1], ``start_pos`` [n_seqs] on the device, or ``lens`` / ``start`` as host arrays), "plain" = the float
+    kernel with one block per (token, head), "auto" = the first that applies."""
+    if kernel == "auto":
+        kernel = "mma" if latent_attention_mma_applies(q_lat, kr, rot) else "plain"
+    if kernel == "plain":
+        return latent_attention_plain(q_lat, pool, layer, out, positions, seq_of_token, slots, block_table, nh, kr, rot,
+                                      page_size, scale, sink, gates, status)
+    if kernel != "mma":
+        raise KernelError(f"latent_attention: no kernel named {kernel!r}")
+    if not latent_attention_mma_applies(q_lat, kr, rot):
+        raise KernelError("latent_attention: the tensor-core kernel takes bfloat16, kr % 16 == 0, kr <= 512, (kr + rot) % 8 == 0")
+    if q_start is None:
+        import numpy as np
+        lens = np.asarray(lens, dtype=np.int64)
+        n_seqs = len(lens)
+        q_start = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=q_lat.device)
+        start_pos = torch.tensor(np.asarray(start), dtype=torch.int32, device=q_lat.device)
+    assert q_lat.is_contiguous() and out.is_contiguous() and out.shape == (q_lat.shape[0], nh * kr)
+    stride, offset = _latent_pool(pool, layer, kr, rot, page_size)
+    if gates is not None:
+        assert gates.dtype == q_lat.dtype and gates.stride(1) == 1 and gates.shape == (q_lat.shape[0], nh)
+    _check(lib().st_latent_attention_mma(_p(q_lat), _p(pool), stride, offset, _p(out), _p(positions), _p(q_start),
+                                         _p(start_pos), _p(slots), _p(block_table), block_table.shape[1],
+                                         q_lat.shape[0], n_seqs, nh, kr, rot, page_size, _p(sink), _p(gates),
+                                         gates.stride(0) if gates is not None else 0, _f(scale), _p(status), _stream()),
+           "latent_attention_mma")
+    return out
+
+
 # ------------------------------------------------------------ grouped products, mixtures of experts
 def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_groups: int, k_dim: int, n_out: int,
                a_goff: int, c_goff: int) -> torch.Tensor:
@@ -919,10 +962,23 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_groups: in
     assert a.dim() == 2 and out.dim() == 2 and a.shape[0] == out.shape[0] and a.stride(1) == 1 and out.stride(1) == 1
     assert w.is_contiguous() and w.shape == (n_groups, n_out, k_dim) and a.dtype == w.dtype
     ll = ctypes.c_longlong
-    _check(lib().st_gemm_grouped_plain(_p(a), _p(w), _p(out), n_groups, a.shape[0], n_out, k_dim, 0, 0, ll(a.stride(0)),
-                                       ll(a_goff), ll(out.stride(0)), ll(c_goff), ll(n_out * k_dim), None, None, None, 0,
-                                       None, 1, _dt(a), int(out.dtype == torch.float32), _stream()), "gemm_heads")
+    args = (_p(a), _p(w), _p(out), n_groups, a.shape[0], n_out, k_dim, 0, 0, ll(a.stride(0)), ll(a_goff), ll(out.stride(0)),
+            ll(c_goff), ll(n_out * k_dim), None, None, None, 0, None, 1)
+    if _grouped_mma(a, k_dim, a.stride(0), a_goff, n_out * k_dim):
+        _check(lib().st_gemm_grouped_mma(*args, int(out.dtype == torch.float32), _stream()), "gemm_heads")
+    else:
+        _check(lib().st_gemm_grouped_plain(*args, _dt(a), int(out.dtype == torch.float32), _stream()), "gemm_heads")
     return out
+
+
+# False: the grouped products of bfloat16 models run on the plain kernel too (measurements, tests)
+GROUPED_MMA = True
+
+
+def _grouped_mma(a: torch.Tensor, k_dim: int, lda: int, a_goff: int, w_gstride: int) -> bool:
+    return (GROUPED_MMA and a.dtype == torch.bfloat16
+            and bool(lib().st_gemm_grouped_mma_applies(k_dim, ctypes.c_longlong(lda), ctypes.c_longlong(a_goff),
+                                                       ctypes.c_longlong(w_gstride))))
 
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, positions: Optional[torch.Tensor] = None,
@@ -976,12 +1032,13 @@ def gemm_experts(a: torch.Tensor, w: torch.Tensor, order: ExpertOrder, gather: b
     n_out = w.shape[1] // 2 if gated else w.shape[1]
     out = torch.empty((order.n_items, n_out), dtype=a.dtype, device=a.device)
     ll = ctypes.c_longlong
-    _check(lib().st_gemm_grouped_plain(_p(a), _p(w), _p(out), w.shape[0], order.n_items, n_out, w.shape[2], int(gated),
-                                       ACT_CODES[act], ll(a.stride(0)), ll(0), ll(n_out), ll(0),
-                                       ll(w.shape[1] * w.shape[2]), _p(order.offsets), _p(order.tile_group),
-                                       _p(order.tile_row0), order.tile_group.numel(),
-                                       _p(order.sorted) if gather else None, order.top if gather else 1, _dt(a), 0,
-                                       _stream()), "gemm_experts")
+    args = (_p(a), _p(w), _p(out), w.shape[0], order.n_items, n_out, w.shape[2], int(gated), ACT_CODES[act], ll(a.stride(0)),
+            ll(0), ll(n_out), ll(0), ll(w.shape[1] * w.shape[2]), _p(order.offsets), _p(order.tile_group),
+            _p(order.tile_row0), order.tile_group.numel(), _p(order.sorted) if gather else None, order.top if gather else 1)
+    if _grouped_mma(a, w.shape[2], a.stride(0), 0, w.shape[1] * w.shape[2]):
+        _check(lib().st_gemm_grouped_mma(*args, 0, _stream()), "gemm_experts")
+    else:
+        _check(lib().st_gemm_grouped_plain(*args, _dt(a), 0, _stream()), "gemm_experts")
     return out
 
 

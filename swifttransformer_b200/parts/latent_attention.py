@@ -25,8 +25,7 @@ import torch
 
 from .. import ops
 from ..weights.spec import GAIN, MATRIX, VECTOR, ParamSpec
-from .attention import PagedAttentionPlan
-from .base import MIXERS, Delta, Mixer, PagedKVSpec, StepPlan
+from .base import MIXERS, Delta, Mixer, PagedKVSpec
 
 
 @MIXERS.register("latent_attention")
@@ -43,7 +42,6 @@ class LatentAttention(Mixer):
         if qk_position is not None and qk_position.dims > self.rot:
             raise ValueError("more rotated dimensions than the rotated part has")
         self.w_in = self.w_uq = self.w_ukt = self.w_uv = self.w_o = self.q_norm = self.kv_norm = self.sink = None
-        self._plan: Optional[PagedAttentionPlan] = None
 
     @property
     def has_gate(self) -> bool:
@@ -94,9 +92,9 @@ class LatentAttention(Mixer):
             ops.latent_q_rotate(q, q_lat, ctx.positions, inv_freq, rot_dims, H, self.dim, self.rot, self.kr)
         o_lat = torch.empty((n, H * self.kr), dtype=h.dtype, device=h.device)
         gates = proj[:, self.qr + kd:self.qr + kd + H] if self.has_gate else None
-        ops.latent_attention_plain(q_lat, cache.pool, cache.layer, o_lat, ctx.positions, ctx.seq_of_token, ctx.slots,
-                                   cache.block_table, H, self.kr, self.rot, cache.page_size, self.scale, self.sink,
-                                   gates, status=ctx.status)
+        ops.latent_attention(q_lat, cache.pool, cache.layer, o_lat, ctx.positions, ctx.seq_of_token, ctx.slots,
+                             cache.block_table, H, self.kr, self.rot, cache.page_size, self.scale, self.sink, gates,
+                             status=ctx.status, q_start=ctx.q_start, start_pos=ctx.start_pos, n_seqs=ctx.n_seqs)
         o = torch.empty((n, H * self.vdim), dtype=h.dtype, device=h.device)
         ops.gemm_heads(o_lat, self.w_uv, o, H, self.kr, self.vdim, self.kr, self.vdim)
         return Delta(ops.linear(o, self.w_o))

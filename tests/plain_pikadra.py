@@ -110,7 +110,7 @@ def latent_attention(h, w, p, mx, eps, positions=None):
     """h [T, width] -> [T, width]; p is the tensor prefix '<layer>.mix.', mx the mixer's sizes and constants."""
     T = h.shape[0]
     H, d, r, vd, kr = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
-    rot = mx["rot"]
+    rot = mx.get("rot") or {"dims": 0, "base": 1.0}          # no rotated part: nothing is turned
     pos = np.arange(T) if positions is None else np.asarray(positions)
     cq = weighted_norm(h @ w[p + "dq"].T, w[p + "dq.norm"], eps)
     q = (cq @ w[p + "uq"].T).reshape(T, H, d + r)

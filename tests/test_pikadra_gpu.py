@@ -1,0 +1,608 @@
+"""The Pikadra design on the GPU against the plain implementation (tests/plain_pikadra.py).
+
+Mechanisms alone (the kernels driven directly over a small paged cache, with inputs made so that a single key, the
+sink or an edge decides the result), then whole models of several small configurations through the trace replay
+(whole prompts, token-by-token decoding, portions down to two tokens, mixed batches with pages and slots used
+again) and through ``LLMEngine.generate``.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_pikadra as pp
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+TD = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.tensor(np.asarray(a), dtype=dtype, device="cuda")
+
+
+def ints(a):
+    return torch.tensor(np.asarray(a), dtype=torch.int32, device="cuda")
+
+
+def bf16_round(a):
+    """float64 array with values that bfloat16 holds exactly."""
+    return torch.tensor(np.asarray(a), dtype=torch.float32).to(torch.bfloat16).double().numpy()
+
+
+class Step:
+    """The index arrays of one step for given (slot, start, n) entries, as the step function lays them out,
+    with padding tokens at position -1 behind."""
+
+    def __init__(self, entries, pad_tokens=0):
+        pos, seq, slots = [], [], []
+        for i, (slot, start, n) in enumerate(entries):
+            pos += list(range(start, start + n))
+            seq += [i] * n
+            slots.append(slot)
+        self.n = len(pos)
+        pos += [-1] * pad_tokens
+        seq += [0] * pad_tokens
+        self.n_rows = len(pos)
+        self.positions, self.seq, self.slots = ints(pos), ints(seq), ints(slots)
+        self.lens = np.array([n for _, _, n in entries], dtype=np.int32)
+        self.start = np.array([s for _, s, _ in entries], dtype=np.int32)
+
+
+def portions(total, sizes):
+    out, pos, k = [], 0, 0
+    while pos < total:
+        n = min(sizes[k % len(sizes)], total - pos)
+        out.append((pos, n))
+        pos += n
+        k += 1
+    return out
+
+
+# ------------------------------------------------------------------------------------------ small row kernels
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_concat_rows_and_logit_cap(dtype):
+    from swifttransformer_b200 import ops
+    rng = np.random.default_rng(0)
+    a, b = rng.normal(size=(7, 13)), bf16_round(rng.normal(size=(7, 5)))
+    out = ops.concat_rows(dev(a), dev(b, TD[dtype])).float().cpu().numpy()
+    tol = 1e-6 if dtype == "float32" else 1e-2
+    assert out.shape == (7, 18) and np.abs(out[:, :13] - a).max() < tol * 4 and np.abs(out[:, 13:] - b).max() == 0
+    x = rng.normal(size=(3, 33)) * 40
+    got = ops.scale_softcap(dev(x), 0.25, 7.0).cpu().numpy()
+    assert np.abs(got - 7.0 * np.tanh(x * 0.25 / 7.0)).max() < 1e-5
+    got = ops.scale_softcap(dev(x), 0.5, 0.0).cpu().numpy()
+    assert np.abs(got - 0.5 * x).max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("G,k,n,rows", [(3, 10, 7, 5), (1, 64, 64, 70), (5, 33, 130, 129), (2, 128, 16, 1)])
+def test_one_product_per_head(dtype, G, k, n, rows):
+    from swifttransformer_b200 import ops
+    rng = np.random.default_rng(G * 7 + k)
+    extra = 3                                   # columns of a head that the product does not read
+    a = bf16_round(rng.normal(size=(rows, G, k + extra)))
+    w = bf16_round(rng.normal(size=(G, n, k)))
+    out = torch.full((rows, G * (n + 2)), 9.0, dtype=TD[dtype], device="cuda")
+    ops.gemm_heads(dev(a.reshape(rows, -1), TD[dtype]), dev(w, TD[dtype]), out, G, k, n, k + extra, n + 2)
+    got = out.float().cpu().numpy().reshape(rows, G, n + 2)
+    ref = np.einsum("rgk,gnk->rgn", a[..., :k], w)
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    assert np.abs(got[..., :n] - ref).max() < tol * np.abs(ref).max()
+    assert np.all(got[..., n:] == 9.0)          # what lies between the heads' columns is not touched
+
+
+# ------------------------------------------------------------------------------------------ latent attention
+def rotate_ref(u, pos, dims, base):
+    return pp.rotate_halves(u, pos, dims, base) if dims else u
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("qr,kr,rot,dims,H,d", [(9, 14, 4, 4, 3, 6), (80, 160, 8, 6, 2, 16), (5, 7, 0, 0, 1, 3), (33, 64, 16, 16, 4, 32)])
+def test_latent_prepare_and_query_rotation(dtype, qr, kr, rot, dims, H, d):
+    from swifttransformer_b200 import ops
+    rng = np.random.default_rng(qr)
+    ps, eps, base = 4, 1e-3, 50.0
+    st = Step([(1, 5, 6), (0, 0, 3)], pad_tokens=2)
+    proj = bf16_round(rng.normal(size=(st.n_rows, qr + kr + rot + H)) * 2)
+    qw, kw = rng.uniform(0.5, 1.5, qr), rng.uniform(0.5, 1.5, kr)
+    inv = np.array([base ** (-2.0 * i / dims) for i in range(dims // 2)] or [0.0])
+    pool = torch.zeros((8, 2, ps * (kr + rot)), dtype=TD[dtype], device="cuda")
+    table = ints([[5, 2, -1, -1], [7, 0, 3, -1]])
+    cq = torch.zeros((st.n_rows, qr), dtype=TD[dtype], device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.latent_prepare(dev(proj, TD[dtype]), qr, dev(qw), dev(kw), eps, dev(inv), dims, cq, pool, 1, st.positions, st.seq,
+                       st.slots, table, kr, rot, ps, status)
+    assert int(status.item()) == 0
+    pos = st.positions.cpu().numpy()[:st.n]
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    ref_q = pp.weighted_norm(proj[:st.n, :qr], qw, eps)
+    assert np.abs(cq.float().cpu().numpy()[:st.n] - ref_q).max() < tol * np.abs(ref_q).max()
+    ref_c = pp.weighted_norm(proj[:st.n, qr:qr + kr], kw, eps)
+    ref_r = rotate_ref(proj[:st.n, qr + kr:qr + kr + rot], pos, dims, base)
+    pages = {1: [7, 0, 3], 0: [5, 2]}
+    got_pool = pool.float().cpu().numpy().reshape(8, 2, ps, kr + rot)
+    for t in range(st.n):
+        slot = 1 if t < 6 else 0
+        row = got_pool[pages[slot][pos[t] // ps], 1, pos[t] % ps]
+        assert np.abs(row[:kr] - ref_c[t]).max() < tol * np.abs(ref_c).max()
+        if rot:
+            assert np.abs(row[kr:] - ref_r[t]).max() < tol * np.abs(ref_r).max() + 1e-6
+    assert float(got_pool[:, 0].max()) == 0.0            # the other cache entry of the pages stays as it was
+    # the queries' rotated parts
+    q = bf16_round(rng.normal(size=(st.n_rows, H, d + rot)))
+    q_lat = torch.zeros((st.n_rows, H * (kr + rot)), dtype=TD[dtype], device="cuda")
+    if rot:
+        ops.latent_q_rotate(dev(q.reshape(st.n_rows, -1), TD[dtype]), q_lat, st.positions, dev(inv), dims, H, d, rot, kr)
+        got = q_lat.float().cpu().numpy().reshape(st.n_rows, H, kr + rot)
+        ref = rotate_ref(q[:st.n, :, d:], pos, dims, base)
+        assert np.abs(got[:st.n, :, kr:] - ref).max() < tol * np.abs(ref).max()
+        assert np.all(got[st.n:] == 0) and np.all(got[:, :, :kr] == 0)
+
+
+class LatentCase:
+    """Rows [latent | shared key part] of a few requests in a paged pool whose pages are dealt out of order and whose
+    unused rows hold large numbers; queries in the latent space, sinks and gate logits."""
+
+    def __init__(self, lengths, H, kr, rot, ps, seed, dtype):
+        rng = np.random.default_rng(seed)
+        self.H, self.kr, self.rot, self.ps, self.dtype = H, kr, rot, ps, dtype
+        self.kd = kr + rot
+        self.lengths = lengths
+        self.rows = [bf16_round(rng.normal(size=(n, self.kd))) for n in lengths]
+        self.q = [bf16_round(rng.normal(size=(n, H, self.kd))) for n in lengths]
+        self.gate = [bf16_round(rng.normal(size=(n, H))) for n in lengths]
+        self.sink = rng.normal(size=H) * 2
+        self.scale = 0.7 / np.sqrt(self.kd)
+        self.max_pages = max((n + ps - 1) // ps for n in lengths) + 1
+        n_pages = sum((n + ps - 1) // ps for n in lengths) + 3
+        self.order = rng.permutation(n_pages)
+        self.table = np.full((len(lengths) + 1, self.max_pages), -1, dtype=np.int32)
+        self.slot = [len(lengths) - i for i in range(len(lengths))]      # slots in another order than requests
+        k = 0
+        for i, n in enumerate(lengths):
+            for j in range((n + ps - 1) // ps):
+                self.table[self.slot[i], j] = self.order[k]
+                k += 1
+        self.n_pages = n_pages
+
+    def write_pool(self):
+        pool = np.full((self.n_pages, 2, self.ps, self.kd), 3e4)
+        for i, rows in enumerate(self.rows):
+            for p in range(len(rows)):
+                pool[self.table[self.slot[i], p // self.ps], 1, p % self.ps] = rows[p]
+        self.pool = dev(pool.reshape(self.n_pages, 2, -1), TD[self.dtype])
+
+    def reference(self, i):
+        n = self.lengths[i]
+        out = np.zeros((n, self.H, self.kr))
+        seen = np.arange(n)[None, :] <= np.arange(n)[:, None]
+        for h in range(self.H):
+            s = np.where(seen, self.q[i][:, h] @ self.rows[i].T * self.scale, -np.inf)
+            out[:, h] = pp.sink_softmax(s, self.sink[h]) @ self.rows[i][:, :self.kr]
+            out[:, h] *= pp.sigmoid(self.gate[i][:, h:h + 1])
+        return out
+
+    def run(self, entries, kernel, pad_tokens=0):
+        """entries: (request, start, n).  -> {request: rows start..start+n-1 of the result}"""
+        from swifttransformer_b200 import ops
+        st = Step([(self.slot[i], s, n) for i, s, n in entries], pad_tokens=pad_tokens)
+        q = np.concatenate([self.q[i][s:s + n] for i, s, n in entries] + [np.full((pad_tokens, self.H, self.kd), 50.0)])
+        g = np.concatenate([self.gate[i][s:s + n] for i, s, n in entries] + [np.zeros((pad_tokens, self.H))])
+        wide = torch.zeros((st.n_rows, self.H + 5), dtype=TD[self.dtype], device="cuda")     # the gates sit inside wider rows
+        wide[:, 2:2 + self.H] = dev(g, TD[self.dtype])
+        out = torch.full((st.n_rows, self.H * self.kr), 77.0, dtype=TD[self.dtype], device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.latent_attention(dev(q.reshape(st.n_rows, -1), TD[self.dtype]), self.pool, 1, out, st.positions, st.seq,
+                             st.slots, ints(self.table), self.H, self.kr, self.rot, self.ps, self.scale, dev(self.sink),
+                             wide[:, 2:2 + self.H], status=status, kernel=kernel, lens=st.lens, start=st.start)
+        assert int(status.item()) == 0
+        o = out.float().cpu().numpy().reshape(st.n_rows, self.H, self.kr)
+        assert np.all(o[st.n:] == 77.0)                  # padding rows are not written
+        res, at = {}, 0
+        for i, s, n in entries:
+            res[i] = o[at:at + n]
+            at += n
+        return res
+
+
+def kernels_for(dtype):
+    return ["plain"] if dtype == "float32" else ["plain", "auto"]
+
+
+def att_tol(dtype):
+    return 2e-5 if dtype == "float32" else 2e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,kr,rot,ps", [(3, 14, 4, 4), (8, 64, 16, 16), (1, 130, 0, 8), (16, 32, 32, 16), (5, 512, 64, 16), (2, 24, 8, 1)])
+def test_latent_attention_whole_in_portions_decoded_and_batched(dtype, H, kr, rot, ps):
+    lengths = [150, 1, 37] if kr < 500 else [70, 3]
+    case = LatentCase(lengths, H, kr, rot, ps, seed=H + kr, dtype=dtype)
+    case.write_pool()
+    for kernel in kernels_for(dtype):
+        refs = [case.reference(i) for i in range(len(lengths))]
+        scale = max(np.abs(r).max() for r in refs)
+
+        def close(got, i, s, what):
+            err = np.abs(got - refs[i][s:s + len(got)]).max(axis=(1, 2))
+            assert err.max() < att_tol(dtype) * scale, (kernel, what, i, s + int(np.argmax(err)), float(err.max()), scale)
+        # each request alone and whole
+        alone = {}
+        for i, n in enumerate(lengths):
+            alone[i] = case.run([(i, 0, n)], kernel)[i]
+            close(alone[i], i, 0, "whole")
+        # all together in one batch, with padding rows behind: the same numbers as alone, beyond rounding
+        got = case.run([(i, 0, n) for i, n in enumerate(lengths)], kernel, pad_tokens=3)
+        for i in got:
+            close(got[i], i, 0, "batch")
+            assert np.abs(got[i] - alone[i]).max() < att_tol(dtype) * scale
+        # portions of several sizes down to two tokens, then single tokens; two requests side by side
+        cuts = [portions(n, (5, 2, 33, 1, 1, 64, 17, 2)) for n in lengths]
+        for k in range(max(len(c) for c in cuts)):
+            entries = [(i, *cuts[i][k]) for i in range(len(lengths)) if k < len(cuts[i])]
+            got = case.run(entries, kernel)
+            for i, s, n in entries:
+                close(got[i], i, s, "portion")
+        # the last tokens one by one
+        for s in range(max(0, lengths[0] - 40), lengths[0]):
+            close(case.run([(0, s, 1)], kernel)[0], 0, s, "decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("ps", [16, 4])
+def test_one_key_decides_far_back_at_page_borders_first_and_never_the_next_one(dtype, ps):
+    """A key made to stand out: the query's result is that key's latent wherever the key stands (hundreds of
+    positions back, on either side of a page border, the very first token) as long as it is not after the query; the
+    key right after the query is never seen, however loud it is."""
+    H, kr, rot, n = 2, 24, 8, 700
+    for kernel in kernels_for(dtype):
+        for key in (0, 1, ps - 1, ps, 3 * ps - 1, 3 * ps, 400, 640, 698, 699):
+            case = LatentCase([n], H, kr, rot, ps, seed=key, dtype=dtype)
+            case.sink[:] = -30.0
+            case.gate[0][:] = 40.0                                  # gate = 1
+            loud = bf16_round(np.sign(case.rows[0][key]) * 8.0)
+            case.rows[0][key] = loud
+            queries = sorted({key - 1, key, key + 1, key + ps, 699} & set(range(n)))
+            for t in queries:
+                case.q[0][t] = loud[None, :] * 4.0                  # score of the loud key: scale * 4 * 64 * 32
+            case.write_pool()
+            for t in queries:
+                for form, (s, cnt) in (("portion", (max(0, t - 20), min(21, t + 1))), ("decoded", (t, 1))):
+                    got = case.run([(0, s, cnt)], kernel)[0][t - s]
+                    if t >= key:
+                        assert np.abs(got - loud[None, :kr]).max() < 0.05, (kernel, form, key, t)
+                    else:
+                        assert np.abs(got).max() < 7.0, (kernel, form, key, t)      # an average of ordinary rows
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sink_takes_its_share_and_has_no_value(dtype):
+    H, kr, rot, ps = 3, 16, 4, 8
+    case = LatentCase([40], H, kr, rot, ps, seed=3, dtype=dtype)
+    case.gate[0][:] = 40.0
+    case.q[0][:] = 0.0                       # every score is 0: uniform weights over t + 1 keys
+    case.sink[:] = [np.log(5.0), -1e4, 0.0]  # counts as 5 keys, as none, as one
+    case.write_pool()
+    for kernel in kernels_for(dtype):
+        got = case.run([(0, 0, 40)], kernel)[0]
+        for t in (0, 1, 7, 8, 39):
+            mean = case.rows[0][:t + 1, :kr].mean(axis=0)
+            for h, extra in enumerate((5.0, 0.0, 1.0)):
+                ref = mean * (t + 1) / (t + 1 + extra)
+                assert np.abs(got[t, h] - ref).max() < 2e-2, (kernel, t, h)
+
+
+# ------------------------------------------------------------------------------------------ mixture of experts
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("E,top,W,ff,shared", [(5, 2, 24, 12, 16), (1, 1, 17, 9, None), (12, 12, 40, 8, 8), (70, 3, 64, 33, None)])
+def test_mixture_of_experts_against_plain(dtype, E, top, W, ff, shared):
+    from swifttransformer_b200 import ops
+    rng = np.random.default_rng(E + top)
+    n = 150
+    h = bf16_round(rng.normal(size=(n, W)))
+    w = {"router": bf16_round(rng.normal(size=(E, W)) * 1.5)}
+    for e in range(E):
+        w[f"e{e}.gate"], w[f"e{e}.up"] = (bf16_round(rng.normal(size=(ff, W)) * 0.3) for _ in range(2))
+        w[f"e{e}.down"] = bf16_round(rng.normal(size=(W, ff)) * 0.3)
+    mlp = {"router": {"experts": E, "top": top}}
+    if shared:
+        mlp["shared"] = {"ff": shared}
+        w["shared.gate"], w["shared.up"] = (bf16_round(rng.normal(size=(shared, W)) * 0.3) for _ in range(2))
+        w["shared.down"] = bf16_round(rng.normal(size=(W, shared)) * 0.3)
+        w["shared.sg"] = bf16_round(rng.normal(size=(1, W)))
+    pos = np.arange(n)
+    pos[[4, 77]] = -1                                                  # padding rows take no expert
+    T = TD[dtype]
+    hd = dev(h, T)
+    experts, weights, gate = ops.moe_route(hd, dev(w["router"]), top, ints(pos), dev(w["shared.sg"][0]) if shared else None)
+    ref_e, ref_w = pp.route(h, w["router"], top)
+    live = pos >= 0
+    assert np.array_equal(experts.cpu().numpy()[live], ref_e[live]) and np.all(experts.cpu().numpy()[~live] == -1)
+    assert np.abs(weights.cpu().numpy()[live] - ref_w[live]).max() < 1e-5
+    order = ops.moe_sort(experts, E)
+    offsets, place, srt = order.offsets.cpu().numpy(), order.place.cpu().numpy(), order.sorted.cpu().numpy()
+    counts = np.bincount(ref_e[live].ravel(), minlength=E)
+    assert np.array_equal(np.diff(offsets), counts)
+    for item, p in enumerate(place):
+        if pos[item // top] < 0:
+            assert p == -1
+        else:
+            e = ref_e[item // top, item % top]
+            assert offsets[e] <= p < offsets[e + 1] and srt[p] == item
+    w_gu = dev(np.stack([np.concatenate([w[f"e{e}.gate"], w[f"e{e}.up"]]) for e in range(E)]), T)
+    w_down = dev(np.stack([w[f"e{e}.down"] for e in range(E)]), T)
+    u = ops.gemm_experts(hd, w_gu, order, gather=True, gated=True, act="silu")
+    y = ops.gemm_experts(u, w_down, order, gather=False)
+    s = None
+    if shared:
+        gu = ops.linear(hd, dev(np.concatenate([w["shared.gate"], w["shared.up"]]), T))
+        s = ops.linear(ops.gated_act(gu, "silu"), dev(w["shared.down"], T))
+    out = ops.moe_combine(y, order, weights, s, gate).cpu().numpy()
+    ref = pp.mixture(h, w, "", mlp)
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    assert np.abs(out[live] - ref[live]).max() < tol * np.abs(ref).max()
+
+
+# ------------------------------------------------------------------------------------------ whole models
+def mixer(heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, dims=None, base=100.0):
+    m = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, scale=scale)
+    if rot_dim:
+        m["rot"] = {"dims": rot_dim if dims is None else dims, "base": base}
+    return m
+
+
+def layer(mx, mlp):
+    return {"type": "latent_attention", "mixer": mx, "mlp": mlp}
+
+
+def moe(ff, experts, top, shared):
+    m = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared:
+        m["shared"] = {"ff": shared}
+    return m
+
+
+CONFIGS = {
+    # a dense layer, then two passes over (a mixture with a shared expert, a layer without feed-forward), then a mixture
+    # without a shared expert; fewer rotated dimensions than the rotated part has
+    "loop": dict(cfg=dict(architecture="Pikadra", vocab=300, width=48, norm={"eps": 1e-5}, embedding={"scale": 5.0},
+                          logit_scale=0.4, logit_softcap=12.0, loop={"start": 1, "stop": 3, "times": 2},
+                          layers=[layer(mixer(4, 12, 8, 10, 20, 16, 0.25), {"kind": "dense", "ff": 64}),
+                                  layer(mixer(2, 16, 4, 24, 32, 12, 0.3, dims=2), moe(24, 6, 2, 40)),
+                                  layer(mixer(4, 12, 8, 10, 20, 16, 0.2, base=7.0), None),
+                                  layer(mixer(3, 8, 6, 8, 10, 30, 0.35), moe(16, 3, 3, None))]),
+                 seed=11, std=0.15, page_size=8),
+    # no loop, no cap, no scales; one head; one expert; sizes that are no multiples of anything; pages of 4
+    "bare": dict(cfg=dict(architecture="Pikadra", vocab=257, width=36, norm={"eps": 1e-4},
+                          layers=[layer(mixer(1, 7, 2, 5, 9, 11, 0.5), moe(10, 1, 1, 14)),
+                                  layer(mixer(5, 6, 0, 9, 13, 7, 0.4), {"kind": "dense", "ff": 50})]),
+                 seed=12, std=0.2, page_size=4),
+    # the loop covers every layer and runs three times: the first pass opens before the first layer
+    "all": dict(cfg=dict(architecture="Pikadra", vocab=128, width=64, norm={"eps": 1e-6}, embedding={"scale": 8.0},
+                         logit_scale=1.0, logit_softcap=5.0, loop={"start": 0, "stop": 2, "times": 3},
+                         layers=[layer(mixer(8, 16, 16, 16, 48, 24, 0.18, base=1000.0), moe(32, 9, 4, 32)),
+                                 layer(mixer(2, 32, 8, 32, 64, 40, 0.15), {"kind": "dense", "ff": 96})]),
+                seed=13, std=0.12, page_size=16),
+}
+
+
+@pytest.fixture(scope="module")
+def pikadra_dirs(tmp_path_factory):
+    """Model folders with random weights; routers and sinks are made loud, so that the choice of experts does not
+    hang on the last bit and a forgotten sink shows."""
+    from swifttransformer_b200.config import PikadraConfig, save_config
+    from swifttransformer_b200.models import build_model_def
+    from swifttransformer_b200.weights.random_init import random_tensors
+    from swifttransformer_b200.weights.safetensors_io import write_safetensors
+    root = tmp_path_factory.mktemp("pikadra")
+    out = {}
+    for name, c in CONFIGS.items():
+        cfg = PikadraConfig.from_dict(c["cfg"])
+        path = str(root / name)
+        save_config(cfg, path)
+        tensors = []
+        for s, t in random_tensors(build_model_def(cfg).param_specs(), c["seed"], c["std"], "cpu"):
+            if s.name.endswith(".router"):
+                t = (t.float() * 6).to(torch.bfloat16)
+            elif s.name.endswith(".sink"):
+                t = (t.float() / c["std"] * 1.5).to(torch.bfloat16)
+            tensors.append((s.name, t))
+        write_safetensors(os.path.join(path, "model.safetensors"), tensors)
+        out[name] = path
+    return out
+
+
+_PLAIN = {}
+
+
+def plain_logits(model_dir, tokens):
+    key = (model_dir, tuple(tokens))
+    if key not in _PLAIN:
+        if model_dir not in _PLAIN:
+            _PLAIN[model_dir] = pp.load_model(model_dir)
+        cfg, w = _PLAIN[model_dir]
+        _PLAIN[key] = pp.forward(cfg, w, tokens)
+    return _PLAIN[key]
+
+
+def requests_for(name, lengths=(150, 1, 23, 97, 64)):
+    vocab = CONFIGS[name]["cfg"]["vocab"]
+    return {f"r{i}": helpers.random_tokens(vocab, n, seed=10 * i + len(name)) for i, n in enumerate(lengths)}
+
+
+def compare(model_dir, reqs, got, dtype, what):
+    """float32: every position within rounding.  bfloat16: rounding of the activations can hand a token to another
+    expert where two scores nearly tie, so a few positions may lie further off; most must be close and none wild."""
+    tol = {"float32": 3e-5, "bfloat16": 5e-2}[dtype]
+    for rid, toks in reqs.items():
+        ref = plain_logits(model_dir, toks)
+        assert got[rid].shape == ref.shape, (what, rid)
+        scale = np.abs(ref).max()
+        err = np.abs(got[rid] - ref).max(axis=1) / scale
+        if dtype == "float32":
+            bad = helpers.first_bad(got[rid], ref, tol * scale)
+            assert bad is None, f"{what}/{dtype}: request {rid} first differs at position {bad[0]} of {len(toks)} by {bad[1]:.3e} of {scale:.3e}"
+        else:
+            assert np.median(err) < tol / 2 and (err > tol).mean() <= 0.1 and err.max() < 8 * tol, \
+                f"{what}/{dtype}: request {rid}: median {np.median(err):.3e}, worst {err.max():.3e} at {int(np.argmax(err))}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("schedule", ["whole", "decode", "portions", "mixed"])
+def test_replay_matches_plain(pikadra_dirs, name, dtype, schedule):
+    from swifttransformer_b200.engine.replay import TraceSession
+    reqs = requests_for(name)
+    steps = {"whole": helpers.trace_whole, "decode": lambda r: helpers.trace_decode_tail(r, tail=45),
+             "portions": helpers.trace_portions, "mixed": lambda r: helpers.trace_mixed(r, seed=1, max_live=3)}[schedule](reqs)
+    need = helpers.live_token_need(steps)
+    s = TraceSession(pikadra_dirs[name], dtype, need, page_size=CONFIGS[name]["page_size"], max_requests=3)
+    got = helpers.replay(s, steps)
+    compare(pikadra_dirs[name], reqs, got, dtype, f"{name}/{schedule}")
+    s.cache.check()
+    assert all(g.pool.num_held == 0 for g in s.cache.groups)
+
+
+def test_residual_stream_after_every_layer_run(pikadra_dirs):
+    """Layer by layer: the float residual rows after every run of a layer (what is still pending included)."""
+    from swifttransformer_b200.engine.replay import TraceSession
+    name = "loop"
+    toks = helpers.random_tokens(CONFIGS[name]["cfg"]["vocab"], 29, seed=5)
+    s = TraceSession(pikadra_dirs[name], "float32", 64, page_size=8, max_requests=1)
+    s.runner.use_cuda_graphs = False
+    got = []
+
+    def hook(i, stream):
+        if s.model.blocks[s.model.layer_order[i].block].mixer is None:
+            return
+        x, p = stream.x.clone(), stream.pending
+        for part in ((p.value,) if p and p.value is not None else ()) + ((p.parts.sum(0),) if p and p.parts is not None else ()):
+            x += part.float()
+        if p and p.bias is not None:
+            x += p.bias
+        got.append(x.cpu().numpy())
+    s.model.after_layer = hook
+    s.run_step([dict(id="a", tokens=toks, want=[28])], ["a"])
+    cfg, w = pp.load_model(pikadra_dirs[name])
+    _, ref = pp.forward(cfg, w, toks, return_layers=True)
+    assert len(got) == len(ref) == 6
+    for i in range(len(ref)):
+        assert np.abs(got[i] - ref[i]).max() < 2e-5 * np.abs(ref[i]).max(), i
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_recorded_and_eager_steps_agree(pikadra_dirs, dtype):
+    from swifttransformer_b200.engine.replay import TraceSession
+    reqs = requests_for("loop", lengths=(70, 9))
+    steps = helpers.trace_mixed(reqs, seed=2, max_live=2)
+    outs = []
+    for graphs in (True, False):
+        s = TraceSession(pikadra_dirs["loop"], dtype, helpers.live_token_need(steps), max_requests=2)
+        s.runner.use_cuda_graphs = graphs
+        outs.append(helpers.replay(s, steps))
+        assert (s.runner.graph_steps + s.runner.padded_graph_steps > 0) == graphs
+    for rid in reqs:
+        tol = 1e-5 if dtype == "float32" else 3e-2
+        err = np.abs(outs[0][rid] - outs[1][rid]).max(axis=1) / np.abs(outs[1][rid]).max()
+        assert err.max() < tol if dtype == "float32" else (np.median(err) < tol and (err > tol).mean() < 0.1)
+
+
+def test_long_decoding_with_pages_and_slots_used_again(pikadra_dirs):
+    """Three requests after one another through the same single slot and a pool that holds only one of them, each
+    decoded token by token for 200 steps after a short prompt."""
+    from swifttransformer_b200.engine.replay import TraceSession
+    name = "all"
+    s = TraceSession(pikadra_dirs[name], "float32", 256, page_size=16, max_requests=1)
+    for k in range(3):
+        toks = helpers.random_tokens(CONFIGS[name]["cfg"]["vocab"], 230, seed=40 + k)
+        rows = [s.run_step([dict(id=k, tokens=toks[:30], want=list(range(30)))]).cpu().numpy().copy()]
+        for t in range(30, 230):
+            rows.append(s.run_step([dict(id=k, tokens=[toks[t]], want=[0])], [k] if t == 229 else []).cpu().numpy().copy())
+        s.check()
+        ref = plain_logits(pikadra_dirs[name], toks)
+        assert np.abs(np.concatenate(rows) - ref).max() < 3e-5 * np.abs(ref).max()
+    assert all(g.pool.num_held == 0 for g in s.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["loop", "bare"])
+def test_greedy_generation_through_the_engine(pikadra_dirs, name, dtype):
+    from swifttransformer_b200.engine.engine import LLMEngine
+    from swifttransformer_b200.sampling.sampler import SamplingParams
+    vocab = CONFIGS[name]["cfg"]["vocab"]
+    prompts = [helpers.random_tokens(vocab, n, seed=n) for n in (5, 31, 1, 18, 44, 9)]
+    eng = LLMEngine(pikadra_dirs[name], dtype=dtype, page_size=CONFIGS[name]["page_size"], num_pages=24,
+                    max_num_seqs=3, max_batch_tokens=48, chunk_size=20, max_seq_len=256)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=12, temperature=0.0))
+    cfg, w = pp.load_model(pikadra_dirs[name])
+    for prompt, out in zip(prompts, outs):
+        toks = list(prompt)
+        tokens = list(out.output if hasattr(out, "output") else out)
+        assert len(tokens) == 12
+        for k, tok in enumerate(tokens):
+            logits = pp.forward(cfg, w, toks)[-1]
+            best = int(np.argmax(logits))
+            if tok != best:
+                # a near tie may fall either way in bfloat16; anything else is a fault
+                gap = logits[best] - logits[tok]
+                assert dtype == "bfloat16" and gap < 0.08 * np.abs(logits).max(), (name, k, tok, best, gap)
+            toks.append(tok)
+
+
+# ------------------------------------------------------------------------------------------ the programs
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_run_gpt_takes_a_pikadra_folder(pikadra_dirs, tmp_path):
+    import subprocess
+    import sys
+    vocab = CONFIGS["loop"]["cfg"]["vocab"]
+    prompts = [helpers.random_tokens(vocab, n, 70 + n) for n in (6, 21)]
+    inp = tmp_path / "in.txt"
+    inp.write_text("\n".join(" ".join(map(str, p)) for p in prompts) + "\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "run_gpt"), pikadra_dirs["loop"], "any", "fp32", str(inp),
+                        "--max_decoding_step", "5", "--num_total_blocks", "64"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    cfg, w = pp.load_model(pikadra_dirs["loop"])
+    lines = [l for l in r.stdout.splitlines() if l.startswith("[")]
+    assert len(lines) == 2
+    for line, p in zip(lines, prompts):
+        got = [int(t) for t in line.split(")")[1].split("(")[0].split()]
+        assert got == pp.greedy(cfg, w, p, 5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program_with_four_slots(pikadra_dirs, tmp_path, dtype):
+    """bin/trace_run with its defaults (four request slots, pages of 16): six requests, at most four live, so slots and
+    pages are handed out again; every wanted row against the plain implementation."""
+    import subprocess
+    import sys
+    name = "loop"
+    reqs = requests_for(name, lengths=(50, 1, 33, 70, 18, 40))
+    steps = helpers.trace_mixed(reqs, seed=3, max_live=4)
+    out = tmp_path / "out"
+    p = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", pikadra_dirs[name], "--dtype", dtype,
+                          "--out", str(out), "--max-tokens", str(helpers.live_token_need(steps))],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    got = {rid: [] for rid in reqs}
+    vocab = CONFIGS[name]["cfg"]["vocab"]
+    for i, st in enumerate(steps):
+        p.stdin.write(json.dumps(dict(st, step=i)) + "\n")
+        p.stdin.flush()
+        assert p.stdout.readline().strip() == f"done {i}", p.stderr.read()[-2000:]
+        arr = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, vocab)
+        k = 0
+        for e in st["entries"]:
+            got[e["id"]].append(arr[k:k + len(e["want"])])
+            k += len(e["want"])
+        assert k == len(arr)
+    p.stdin.close()
+    assert p.wait(timeout=120) == 0
+    compare(pikadra_dirs[name], reqs, {rid: np.concatenate(v) for rid, v in got.items()}, dtype, "trace_run")
