@@ -13,8 +13,9 @@ single-GPU and exits with 2.
 ``--only decode|prefill`` run one small measurement (for profiling); ``--only mixed`` runs a continuous
 batch of requests of random lengths (prompt portions of 512 tokens beside decoded tokens) through
 ``LLMEngine.generate`` and reports tokens per second, steps and preemptions.  ``--only designs`` measures a
-Fanidra model beside an OPT model of equal width, depth and parameter count (prefill, decode, and the device time
-of every operation of one step of each kind; ``--model-name w2048|w4096`` picks one size, ``--layers`` the depth).
+Fanidra model and a Pikadra model beside an OPT model of equal width, depth and parameter count (prefill, decode, and
+the device time of every operation of one step of each kind; ``--model-name w2048|w4096`` picks one size, ``--layers``
+the depth, ``--designs`` which of the three).
 """
 import argparse
 import json
@@ -100,23 +101,30 @@ def prefill_flops(cfg, n_layers, n):
 # Layer sizes for ``--only designs``: a Fanidra model beside an OPT model of the same width, depth and (nearly) the
 # same number of parameters per layer (a gated feed-forward has three matrices: its inner size is two thirds of
 # OPT's).  Every fourth layer of the Fanidra model is the recurrence, the others attention.
+# The Pikadra model of a size: latent attention (key/value latent of 512 + 64 rotated numbers per token), layers with
+# a dense gated feed-forward alternating with mixtures (8 experts, 2 per token, plus a shared expert); parameter bytes
+# per layer within 7 % of OPT's.
 DESIGN_SIZES = {
     "w2048": dict(width=2048, opt_heads=32, opt_ffn=8192, heads=16, kv_heads=4, dim=64, vdim=128, ff=5504,
-                  rec_heads=16, rec_dim=128, rec_vdim=128, block=512),
+                  rec_heads=16, rec_dim=128, rec_vdim=128, block=512,
+                  pk=dict(heads=16, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=768, ff=6336, experts=8, top=2,
+                          expert_ff=512, shared_ff=2048)),
     "w4096": dict(width=4096, opt_heads=32, opt_ffn=16384, heads=32, kv_heads=8, dim=64, vdim=128, ff=10944,
-                  rec_heads=32, rec_dim=128, rec_vdim=128, block=512),
+                  rec_heads=32, rec_dim=128, rec_vdim=128, block=512,
+                  pk=dict(heads=32, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, ff=13184, experts=8, top=2,
+                          expert_ff=1024, shared_ff=4096)),
 }
 
 
 def compare_designs(args, peaks):
-    """Prefill (2048 tokens) and decode (batch 8 behind 512-token prompts) of a Fanidra model and of an OPT model
-    of equal size, random weights, device-timed; and the device time of every operation of one prefill step and one
+    """Prefill (2048 tokens) and decode (batch 8 behind 512-token prompts) of a Fanidra model, a Pikadra model and
+    an OPT model of equal size, random weights, device-timed; and the device time of every operation of one prefill step and one
     decode step launched kernel by kernel.  One JSON line per (size, design)."""
     import gc
     import numpy as np
     import torch
     from swifttransformer_b200 import ops
-    from swifttransformer_b200.config import FanidraConfig, OptConfig
+    from swifttransformer_b200.config import FanidraConfig, OptConfig, PikadraConfig
     from swifttransformer_b200.engine.engine import LLMEngine
     from swifttransformer_b200.engine.step import StepEntry
     from swifttransformer_b200.models import random_model
@@ -140,7 +148,18 @@ def compare_designs(args, peaks):
         opt = OptConfig.from_dict(dict(vocab_size=vocab, hidden_size=z["width"], num_hidden_layers=n_layers,
                                        ffn_dim=z["opt_ffn"], num_attention_heads=z["opt_heads"],
                                        max_position_embeddings=4096))
-        return {"fanidra": fan, "opt": opt}
+        k = z["pk"]
+        mix = dict(heads=k["heads"], dim=k["dim"], rot_dim=k["rot"], vdim=k["vdim"], kv_rank=k["kv_rank"],
+                   q_rank=k["q_rank"], scale=(k["dim"] + k["rot"]) ** -0.5, rot={"dims": k["rot"], "base": 10000.0})
+        dense = {"type": "latent_attention", "mixer": mix, "mlp": {"kind": "dense", "ff": k["ff"]}}
+        routed = {"type": "latent_attention", "mixer": mix,
+                  "mlp": {"kind": "moe", "expert": {"ff": k["expert_ff"]}, "router": {"experts": k["experts"], "top": k["top"]},
+                          "shared": {"ff": k["shared_ff"]}}}
+        pik = PikadraConfig.from_dict(dict(architecture="Pikadra", vocab=vocab, width=z["width"], norm={"eps": 1e-6},
+                                           embedding={"scale": 8.0}, logit_scale=0.25, logit_softcap=30.0,
+                                           layers=[routed if i % 2 else dense for i in range(n_layers)]))
+        all_designs = {"fanidra": fan, "pikadra": pik, "opt": opt}
+        return {d: c for d, c in all_designs.items() if not args.designs or d in args.designs.split(",")}
 
     def engine(model, graphs=True):
         gc.collect()
@@ -241,6 +260,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the model has (0: all)")
+    ap.add_argument("--designs", default="", help="with --only designs: which designs to measure, with commas between "
+                    "them (fanidra, pikadra, opt; default: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-big", action="store_true", help="skip the OPT-6.7B and OPT-30B points (13 and 60 GB of random weights)")
     ap.add_argument("--launch-floor", action="store_true",

@@ -21,7 +21,9 @@ TIMED = ("embed", "add_positions", "add_norm", "bias_act", "scatter_i32", "gathe
          "gemm_skinny", "gemm_stream_tc", "norm_linear", "linear_add", "norm_qkv_linear_to_cache", "qkv_linear_to_cache",
          "qkv_to_cache", "attention_plain", "attention_decode", "attention_decode_qkv", "attention_prefill",
          "linear_parts", "argmax", "sample", "conv_residual", "conv_state_update", "norm_add", "gated_act",
-         "diff_qkv_prepare", "diff_attention_plain", "diff_attention_single", "diff_attention_tiles", "hgrn2_scan")
+         "diff_qkv_prepare", "diff_attention_plain", "diff_attention_single", "diff_attention_tiles", "hgrn2_scan",
+         "latent_prepare", "latent_q_rotate", "latent_attention", "gemm_heads", "moe_route", "moe_sort", "gemm_experts",
+         "moe_combine", "concat_rows", "scale_softcap")
 
 _originals: Dict[str, object] = {}
 _events: List[Tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
