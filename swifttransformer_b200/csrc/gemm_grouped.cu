@@ -145,12 +145,13 @@ ST_EXPORT int st_gemm_grouped_plain(const void* a, const void* w, void* c, int n
 
 #define GM_BK 32
 #define GM_LD (GM_BK + 8)
+#define GM_STAGES 3
 
 template <typename TO, bool GATED>
 __global__ void __launch_bounds__(128)
 gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TO* __restrict__ c, GroupedShape sh) {
-    __shared__ __align__(16) bf16 sa[2][GG_BM][GM_LD];
-    __shared__ __align__(16) bf16 sw[2][GATED ? 2 * GG_BN : GG_BN][GM_LD];
+    __shared__ __align__(16) bf16 sa[GM_STAGES][GG_BM][GM_LD];
+    __shared__ __align__(16) bf16 sw[GM_STAGES][GATED ? 2 * GG_BN : GG_BN][GM_LD];
     __shared__ int srow[GG_BM];
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
@@ -205,18 +206,19 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
     const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
     const int n_k = (sh.k_dim + GM_BK - 1) / GM_BK;
-    load(0, 0);
-    cp_async_commit();
+    // three stages: two tiles of k under way while one is multiplied (a group is committed every turn, so that
+    // "all but the newest" always means the tile about to be used)
+#pragma unroll
+    for (int p = 0; p < GM_STAGES - 1; ++p) {
+        if (p < n_k) load(p * GM_BK, p);
+        cp_async_commit();
+    }
     for (int kt = 0; kt < n_k; ++kt) {
-        const int stage = kt & 1;
-        if (kt + 1 < n_k) {
-            load((kt + 1) * GM_BK, stage ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int stage = kt % GM_STAGES;
+        cp_async_wait<GM_STAGES - 2>();
         __syncthreads();
+        if (kt + GM_STAGES - 1 < n_k) load((kt + GM_STAGES - 1) * GM_BK, (kt + GM_STAGES - 1) % GM_STAGES);
+        cp_async_commit();
 #pragma unroll
         for (int kk = 0; kk < GM_BK; kk += 16) {
             uint32_t af[2][4];
@@ -242,7 +244,6 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
                 }
             }
         }
-        __syncthreads();
     }
     const int gq = lane >> 2, tq = lane & 3;
 #pragma unroll

@@ -42,6 +42,7 @@ def lib() -> ctypes.CDLL:
         except OSError as e:
             raise KernelError(f"cannot load {path}: {e}") from None
         _LIB.st_attention_decode_scratch_floats.restype = ctypes.c_longlong
+        _LIB.st_latent_attention_mma_scratch.restype = ctypes.c_longlong
         _LIB.st_uniform_host.restype = ctypes.c_float
         _LIB.st_uniform_host.argtypes = [ctypes.c_longlong, ctypes.c_longlong]
     return _LIB
@@ -922,11 +923,14 @@ def latent_attention(q_lat: torch.Tensor, pool: torch.Tensor, layer: int, out: t
                      rot: int, page_size: int, scale: float, sink: Optional[torch.Tensor] = None,
                      gates: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, kernel: str = "auto",
                      q_start: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None, n_seqs: int = 0,
-                     lens=None, start=None) -> torch.Tensor:
+                     lens=None, start=None, scratch=None, n_splits: Optional[int] = None) -> torch.Tensor:
     """Latent attention of the step's queries (see ``latent_attention_plain`` for the arguments).  kernel: "mma" = the
     tensor-core kernel over tiles of 64 (token, head) rows (bfloat16; it needs the step's requests: ``q_start``
     [n_seqs + 1], ``start_pos`` [n_seqs] on the device, or ``lens`` / ``start`` as host arrays), "plain" = the float
-    kernel with one block per (token, head), "auto" = the first that applies."""
+    kernel with one block per (token, head), "auto" = the first that applies.  Steps whose tiles do not fill the device
+    (single tokens, short portions) have their key ranges cut into ``n_splits`` parts (None: chosen from the step's
+    shape) whose partial rows meet in a second small kernel; ``scratch``: a function n -> float32 tensor of at least n
+    elements for them (None: allocated here)."""
     if kernel == "auto":
         kernel = "mma" if latent_attention_mma_applies(q_lat, kr, rot) else "plain"
     if kernel == "plain":
@@ -946,10 +950,19 @@ def latent_attention(q_lat: torch.Tensor, pool: torch.Tensor, layer: int, out: t
     stride, offset = _latent_pool(pool, layer, kr, rot, page_size)
     if gates is not None:
         assert gates.dtype == q_lat.dtype and gates.stride(1) == 1 and gates.shape == (q_lat.shape[0], nh)
+    n = q_lat.shape[0]
+    if n_splits is None:
+        n_splits = int(lib().st_latent_attention_mma_splits(n, n_seqs, nh))
+    partial = None
+    if n_splits > 1:
+        need = int(lib().st_latent_attention_mma_scratch(n, n_seqs, nh, kr, n_splits))
+        partial = scratch(need) if scratch is not None else torch.empty(need, dtype=torch.float32, device=q_lat.device)
+        assert partial.dtype == torch.float32 and partial.numel() >= need
     _check(lib().st_latent_attention_mma(_p(q_lat), _p(pool), stride, offset, _p(out), _p(positions), _p(q_start),
                                          _p(start_pos), _p(slots), _p(block_table), block_table.shape[1],
-                                         q_lat.shape[0], n_seqs, nh, kr, rot, page_size, _p(sink), _p(gates),
-                                         gates.stride(0) if gates is not None else 0, _f(scale), _p(status), _stream()),
+                                         n, n_seqs, nh, kr, rot, page_size, _p(sink), _p(gates),
+                                         gates.stride(0) if gates is not None else 0, _f(scale), n_splits, _p(partial),
+                                         _p(status), _stream()),
            "latent_attention_mma")
     return out
 

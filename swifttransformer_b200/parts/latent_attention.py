@@ -94,7 +94,8 @@ class LatentAttention(Mixer):
         gates = proj[:, self.qr + kd:self.qr + kd + H] if self.has_gate else None
         ops.latent_attention(q_lat, cache.pool, cache.layer, o_lat, ctx.positions, ctx.seq_of_token, ctx.slots,
                              cache.block_table, H, self.kr, self.rot, cache.page_size, self.scale, self.sink, gates,
-                             status=ctx.status, q_start=ctx.q_start, start_pos=ctx.start_pos, n_seqs=ctx.n_seqs)
+                             status=ctx.status, q_start=ctx.q_start, start_pos=ctx.start_pos, n_seqs=ctx.n_seqs,
+                             scratch=ctx.scratch_f32)
         o = torch.empty((n, H * self.vdim), dtype=h.dtype, device=h.device)
         ops.gemm_heads(o_lat, self.w_uv, o, H, self.kr, self.vdim, self.kr, self.vdim)
         return Delta(ops.linear(o, self.w_o))

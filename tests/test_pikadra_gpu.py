@@ -199,9 +199,14 @@ class LatentCase:
         wide[:, 2:2 + self.H] = dev(g, TD[self.dtype])
         out = torch.full((st.n_rows, self.H * self.kr), 77.0, dtype=TD[self.dtype], device="cuda")
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
-        ops.latent_attention(dev(q.reshape(st.n_rows, -1), TD[self.dtype]), self.pool, 1, out, st.positions, st.seq,
+        name, _, parts = kernel.partition(":")
+        qd = dev(q.reshape(st.n_rows, -1), TD[self.dtype])
+        if name == "mma" and not ops.latent_attention_mma_applies(qd, self.kr, self.rot):
+            name = "plain"                               # sizes the tensor-core kernel does not take
+        ops.latent_attention(qd, self.pool, 1, out, st.positions, st.seq,
                              st.slots, ints(self.table), self.H, self.kr, self.rot, self.ps, self.scale, dev(self.sink),
-                             wide[:, 2:2 + self.H], status=status, kernel=kernel, lens=st.lens, start=st.start)
+                             wide[:, 2:2 + self.H], status=status, kernel=name, lens=st.lens, start=st.start,
+                             n_splits=int(parts) if parts else None)
         assert int(status.item()) == 0
         o = out.float().cpu().numpy().reshape(st.n_rows, self.H, self.kr)
         assert np.all(o[st.n:] == 77.0)                  # padding rows are not written
@@ -213,7 +218,9 @@ class LatentCase:
 
 
 def kernels_for(dtype):
-    return ["plain"] if dtype == "float32" else ["plain", "auto"]
+    """float32: the plain kernel.  bfloat16: also the tensor-core kernel, uncut, with its own choice of parts, and with
+    the key ranges cut into 5 parts (more than some requests have key tiles)."""
+    return ["plain"] if dtype == "float32" else ["plain", "auto", "mma:1", "mma:5"]
 
 
 def att_tol(dtype):
