@@ -11,8 +11,9 @@
 // Epilogue: none, or "gated": w[g] holds 2 * n_out rows, gate rows first, and c = act(gate) * up.
 //
 // gemm_grouped_mma: bfloat16 on the warp-level tensor cores (mma.sync m16n8k16, float accumulation): tiles of 64 rows
-// x 64 outputs x 32 of k, four warps of 32 x 32 each, rows gathered and weights streamed by 16-byte asynchronous
-// copies in two stages; k, the row strides and the group offsets must be multiples of 8 elements.
+// x 64 outputs x 64 of k, four warps of 32 x 32 each, rows gathered and weights streamed by 16-byte asynchronous
+// copies in three stages (two tiles of k under way per block: steps of few tokens are bound by the weights' way from
+// memory, and what a block has in flight decides the rate); k, the row strides and the group offsets must be multiples of 8 elements.
 // gemm_grouped_plain: float arithmetic for either storage type; every output element is one chain of fused
 // multiply-adds over k in ascending order whatever rows share its tile (the 32-bit path, and the plain twin).
 #include "common.cuh"
@@ -143,15 +144,17 @@ ST_EXPORT int st_gemm_grouped_plain(const void* a, const void* w, void* c, int n
                          (const bf16*)w, (bf16*)c, sh);
 }
 
-#define GM_BK 32
+#define GM_BK 64
 #define GM_LD (GM_BK + 8)
 #define GM_STAGES 3
 
 template <typename TO, bool GATED>
 __global__ void __launch_bounds__(128)
 gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TO* __restrict__ c, GroupedShape sh) {
-    __shared__ __align__(16) bf16 sa[GM_STAGES][GG_BM][GM_LD];
-    __shared__ __align__(16) bf16 sw[GM_STAGES][GATED ? 2 * GG_BN : GG_BN][GM_LD];
+    extern __shared__ __align__(16) unsigned char gm_smem[];
+    constexpr int WROWS = GATED ? 2 * GG_BN : GG_BN;
+    bf16 (*sa)[GG_BM][GM_LD] = reinterpret_cast<bf16 (*)[GG_BM][GM_LD]>(gm_smem);
+    bf16 (*sw)[WROWS][GM_LD] = reinterpret_cast<bf16 (*)[WROWS][GM_LD]>(gm_smem + sizeof(bf16) * GM_STAGES * GG_BM * GM_LD);
     __shared__ int srow[GG_BM];
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
@@ -178,15 +181,15 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
     const bf16* wg = w + (long long)g * sh.w_gstride;
     const bf16* ag = a + g * sh.a_goff;
     auto load = [&](int k0, int stage) {
-        // 64 rows x 4 chunks of 8 per operand
-        for (int ch = tid; ch < GG_BM * 4; ch += 128) {
-            const int r = ch >> 2, kc = (ch & 3) * 8;
+        // 64 rows x 8 chunks of 8 per operand
+        for (int ch = tid; ch < GG_BM * 8; ch += 128) {
+            const int r = ch >> 3, kc = (ch & 7) * 8;
             const int ar = srow[r];
             const bool ok = ar >= 0 && k0 + kc < sh.k_dim;
             cp_async16(&sa[stage][r][kc], ok ? ag + (long long)ar * sh.lda + k0 + kc : a, ok);
         }
-        for (int ch = tid; ch < GG_BN * 4 * (GATED ? 2 : 1); ch += 128) {
-            const int r = ch >> 2, kc = (ch & 3) * 8;
+        for (int ch = tid; ch < GG_BN * 8 * (GATED ? 2 : 1); ch += 128) {
+            const int r = ch >> 3, kc = (ch & 7) * 8;
             const int n = col0 + (r & (GG_BN - 1)) + (r >= GG_BN ? sh.n_out : 0);
             const bool ok = col0 + (r & (GG_BN - 1)) < sh.n_out && k0 + kc < sh.k_dim;
             cp_async16(&sw[stage][r][kc], ok ? wg + (long long)n * sh.k_dim + k0 + kc : w, ok);
@@ -278,17 +281,26 @@ ST_EXPORT int st_gemm_grouped_mma(const void* a, const void* w, void* c, int n_g
     dim3 grid((n_out + GG_BN - 1) / GG_BN, offsets ? n_tiles : (n_rows + GG_BM - 1) / GG_BM, offsets ? 1 : n_groups);
     if (grid.y > 65535 || grid.z > 65535) return ST_ERR_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem_g = sizeof(bf16) * GM_STAGES * (GG_BM + 2 * GG_BN) * GM_LD, smem_p = sizeof(bf16) * GM_STAGES * (GG_BM + GG_BN) * GM_LD;
+    static bool set = false;
+    if (!set) {
+        cudaFuncSetAttribute(gemm_grouped_mma_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_g);
+        cudaFuncSetAttribute(gemm_grouped_mma_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_g);
+        cudaFuncSetAttribute(gemm_grouped_mma_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
+        cudaFuncSetAttribute(gemm_grouped_mma_kernel<bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
+        set = true;
+    }
     if (gated) {
         if (out_f32)
-            return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<float, true>, grid, dim3(128), 0, s, (const bf16*)a,
+            return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<float, true>, grid, dim3(128), smem_g, s, (const bf16*)a,
                                  (const bf16*)w, (float*)c, sh);
-        return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<bf16, true>, grid, dim3(128), 0, s, (const bf16*)a,
+        return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<bf16, true>, grid, dim3(128), smem_g, s, (const bf16*)a,
                              (const bf16*)w, (bf16*)c, sh);
     }
     if (out_f32)
-        return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<float, false>, grid, dim3(128), 0, s, (const bf16*)a,
+        return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<float, false>, grid, dim3(128), smem_p, s, (const bf16*)a,
                              (const bf16*)w, (float*)c, sh);
-    return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<bf16, false>, grid, dim3(128), 0, s, (const bf16*)a,
+    return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<bf16, false>, grid, dim3(128), smem_p, s, (const bf16*)a,
                          (const bf16*)w, (bf16*)c, sh);
 }
 

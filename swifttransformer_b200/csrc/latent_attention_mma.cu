@@ -290,13 +290,17 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
 }
 
 // Finishes the rows of tiles whose key range was cut into parts: the parts' maxima, sums and unnormalised rows
-// are combined, the sink joins the denominator, the gate multiplies.  One block per tile, a warp per row in turn.
-#define LM_MERGE_THREADS 256
+// are combined, the sink joins the denominator, the gate multiplies.  One block per (tile, row): a thread owns pairs
+// of columns and asks for all parts' values at once.
+#define LM_MERGE_THREADS 128
+#define LM_MAX_SPLITS 64
 __global__ void __launch_bounds__(LM_MERGE_THREADS)
 latent_merge_kernel(const float* __restrict__ partial, int n_splits, int dvp, bf16* __restrict__ out,
                     const int* __restrict__ positions, const int* __restrict__ q_start, int n_seqs,
                     const float* __restrict__ sink, const bf16* __restrict__ gates, int gate_ld, int nh, int kr) {
     __shared__ int s_req, s_tile;
+    __shared__ float s_w[LM_MAX_SPLITS];
+    __shared__ float s_k;
     if (threadIdx.x == 0) {
         int tile = blockIdx.x, req = -1;
         for (int i = 0; i < n_seqs; ++i) {
@@ -314,17 +318,15 @@ latent_merge_kernel(const float* __restrict__ partial, int n_splits, int dvp, bf
     const int b = s_req;
     if (b < 0) return;
     const int tok0 = q_start[b], n_rows = (q_start[b + 1] - tok0) * nh, r0 = s_tile * LM_ROWS;
-    if (positions[tok0] < 0) return;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int rows_here = min(LM_ROWS, n_rows - r0);
+    const int row = blockIdx.y;
+    if (positions[tok0] < 0 || r0 + row >= n_rows) return;
+    const int lane = threadIdx.x & 31;
     const size_t stride = (size_t)LM_ROWS * (dvp + 2);
-    const float* base = partial + (size_t)blockIdx.x * n_splits * stride;
-    __shared__ float s_w[LM_MERGE_THREADS / 32][64];
-    for (int row = warp; row < rows_here; row += LM_MERGE_THREADS / 32) {
-        const int tok = tok0 + (r0 + row) / nh, h = (r0 + row) % nh;
-        const float* pr = base + (size_t)row * (dvp + 2);
+    const float* pr = partial + (size_t)blockIdx.x * n_splits * stride + (size_t)row * (dvp + 2);
+    const int tok = tok0 + (r0 + row) / nh, h = (r0 + row) % nh;
+    if (threadIdx.x < 32) {
+        // a lane per part (two turns): maxima, weights, the denominator
         const float snk = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
-        // a lane per part (n_splits <= 64: two turns): maxima, weights, the denominator
         float ms[2], ls[2];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -337,27 +339,26 @@ latent_merge_kernel(const float* __restrict__ partial, int n_splits, int dvp, bf
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const float w = ms[u] > -INFINITY ? exp2f(ms[u] - mf) : 0.f;
-            s_w[warp][lane + 32 * u] = w;
+            s_w[lane + 32 * u] = w;
             den += w * ls[u];
         }
         den = warp_sum(den) + (snk > -INFINITY ? exp2f(snk - mf) : 0.f);
-        __syncwarp();
         float gate = 1.f;
         if (gates) gate = 1.f / (1.f + expf(-load1_cg(gates + (size_t)tok * gate_ld + h)));
-        const float k = den > 0.f ? gate / den : 0.f;
-        bf16* dst = out + ((size_t)tok * nh + h) * kr;
-        for (int col = 2 * lane; col < kr; col += 64) {
-            float2 acc = make_float2(0.f, 0.f);
-#pragma unroll 4
-            for (int sp = 0; sp < n_splits; ++sp) {             // every part wrote its rows (zeros if it was empty)
-                const float w = s_w[warp][sp];
-                const float2 v = __ldcg(reinterpret_cast<const float2*>(pr + sp * stride + 2 + col));
-                acc.x = fmaf(w, v.x, acc.x);
-                acc.y = fmaf(w, v.y, acc.y);
-            }
-            *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(acc.x * k, acc.y * k);
+        if (lane == 0) s_k = den > 0.f ? gate / den : 0.f;
+    }
+    __syncthreads();
+    const float k = s_k;
+    bf16* dst = out + ((size_t)tok * nh + h) * kr;
+    for (int col = 2 * threadIdx.x; col < kr; col += 2 * LM_MERGE_THREADS) {
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll 8
+        for (int sp = 0; sp < n_splits; ++sp) {                 // every part wrote its rows (zeros if it was empty)
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(pr + sp * stride + 2 + col));
+            acc.x = fmaf(s_w[sp], v.x, acc.x);
+            acc.y = fmaf(s_w[sp], v.y, acc.y);
         }
-        __syncwarp();
+        *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(acc.x * k, acc.y * k);
     }
 }
 
@@ -436,7 +437,7 @@ ST_EXPORT int st_latent_attention_mma(const void* q_lat, const void* pool, long 
     LM_LAUNCH(12, 2) LM_LAUNCH(16, 2) LM_LAUNCH(24, 2) LM_LAUNCH(32, 2)
 #undef LM_LAUNCH
     if (rc != 0 || n_splits == 1) return rc;
-    return st_launch_pdl("latent_merge", latent_merge_kernel, dim3((unsigned)tiles), dim3(LM_MERGE_THREADS), 0, s,
+    return st_launch_pdl("latent_merge", latent_merge_kernel, dim3((unsigned)tiles, LM_ROWS), dim3(LM_MERGE_THREADS), 0, s,
                          (const float*)partial, n_splits, nt * 8 * np, (bf16*)out, positions, q_start, n_seqs, sink,
                          (const bf16*)gates, gate_ld, nh, kr);
 }

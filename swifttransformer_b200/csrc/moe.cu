@@ -12,14 +12,14 @@
 // moe_combine: out[t] = sum_k weight[t,k] * y[place[t,k]]  (+ g[t] * shared[t]), in float.
 #include "common.cuh"
 
-#define ROUTE_THREADS 128
+#define ROUTE_THREADS 256
 #define ROUTE_MAX_EXPERTS 1024
 
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ h, int width, const float* __restrict__ w_r, int n_experts, int top,
                  int renorm, const float* __restrict__ w_g, const int* __restrict__ positions,
-                 int* __restrict__ experts, float* __restrict__ weights, float* __restrict__ gate) {
+                 int* __restrict__ experts, float* __restrict__ weights, float* __restrict__ gate, int vec) {
     __shared__ float z[ROUTE_MAX_EXPERTS + 1];
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
@@ -35,7 +35,15 @@ moe_route_kernel(const T* __restrict__ h, int width, const float* __restrict__ w
     for (int e = warp; e < n_rows; e += nwarp) {
         const float* wr = e < n_experts ? w_r + (size_t)e * width : w_g;
         float d = 0.f;
-        for (int i = lane; i < width; i += 32) d = fmaf(load1_cg(row + i), wr[i], d);
+        if (vec) {
+            // four at a time; a lane's partial sums run in the same order whatever the batch
+            for (int i = lane * 4; i < width; i += 128) {
+                const float4 a = load4_cg(row + i), c = *reinterpret_cast<const float4*>(wr + i);
+                d = fmaf(a.x, c.x, fmaf(a.y, c.y, fmaf(a.z, c.z, fmaf(a.w, c.w, d))));
+            }
+        } else {
+            for (int i = lane; i < width; i += 32) d = fmaf(load1_cg(row + i), wr[i], d);
+        }
         d = warp_sum(d);
         if (lane == 0) z[e] = d;
     }
@@ -85,12 +93,13 @@ ST_EXPORT int st_moe_route(const void* h, int n_tokens, int width, const float* 
     if (n_experts <= 0 || top <= 0 || top > n_experts) return ST_ERR_BAD_ARG;
     if (n_experts > ROUTE_MAX_EXPERTS) return ST_ERR_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
+    const int vec = width % 4 == 0 && aligned16(h) && aligned16(w_r) && (!w_g || aligned16(w_g));
     if (dtype == 0)
         return st_launch_pdl("moe_route", moe_route_kernel<float>, dim3(n_tokens), dim3(ROUTE_THREADS), 0, s, (const float*)h,
-                             width, w_r, n_experts, top, renorm, w_g, positions, experts, weights, gate);
+                             width, w_r, n_experts, top, renorm, w_g, positions, experts, weights, gate, vec);
     if (dtype == 1)
         return st_launch_pdl("moe_route", moe_route_kernel<bf16>, dim3(n_tokens), dim3(ROUTE_THREADS), 0, s, (const bf16*)h,
-                             width, w_r, n_experts, top, renorm, w_g, positions, experts, weights, gate);
+                             width, w_r, n_experts, top, renorm, w_g, positions, experts, weights, gate, vec);
     return ST_ERR_BAD_DTYPE;
 }
 
@@ -150,13 +159,31 @@ ST_EXPORT int st_moe_sort(const int* experts, int n_items, int n_experts, int ti
                          n_experts, tile_rows, tile_cap, offsets, sorted, place, tile_group, tile_row0);
 }
 
-template <typename T, typename TO>
+template <typename T, typename TO, bool VEC>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights, int top,
                    const T* __restrict__ shared, const float* __restrict__ gate, int width, TO* __restrict__ out) {
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
     const int t = blockIdx.x;
+    if (VEC) {
+        for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; ++k) {
+                const int p = __ldcg(place + (size_t)t * top + k);
+                if (p < 0) continue;
+                const float w = __ldcg(weights + (size_t)t * top + k);
+                const float4 v = load4_cg(y + (size_t)p * width + e);
+                acc = make_float4(fmaf(w, v.x, acc.x), fmaf(w, v.y, acc.y), fmaf(w, v.z, acc.z), fmaf(w, v.w, acc.w));
+            }
+            if (shared) {
+                const float w = __ldcg(gate + t);
+                const float4 v = load4_cg(shared + (size_t)t * width + e);
+                acc = make_float4(fmaf(w, v.x, acc.x), fmaf(w, v.y, acc.y), fmaf(w, v.z, acc.z), fmaf(w, v.w, acc.w));
+            }
+            store4(out + (size_t)t * width + e, acc);
+        }
+    } else
     for (int e = threadIdx.x; e < width; e += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -172,15 +199,22 @@ ST_EXPORT int st_moe_combine(const void* y, const int* place, const float* weigh
                              const float* gate, int n_tokens, int width, void* out, int dtype, int out_f32, void* stream) {
     if (n_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    int block = (width + 31) / 32 * 32;
+    const bool vec = width % 4 == 0 && aligned16(y) && aligned16(out) && (!shared || aligned16(shared));
+    int block = ((vec ? width / 4 : width) + 31) / 32 * 32;
     if (block > 256) block = 256;
-    if (dtype == 0)
-        return st_launch_pdl("moe_combine", moe_combine_kernel<float, float>, dim3(n_tokens), dim3(block), 0, s,
-                             (const float*)y, place, weights, top, (const float*)shared, gate, width, (float*)out);
+#define MC_LAUNCH(T, TO, VEC)                                                                                           \
+    return st_launch_pdl("moe_combine", moe_combine_kernel<T, TO, VEC>, dim3(n_tokens), dim3(block), 0, s, (const T*)y, \
+                         place, weights, top, (const T*)shared, gate, width, (TO*)out)
+    if (dtype == 0) {
+        if (vec) MC_LAUNCH(float, float, true);
+        MC_LAUNCH(float, float, false);
+    }
     if (dtype != 1) return ST_ERR_BAD_DTYPE;
-    if (out_f32)
-        return st_launch_pdl("moe_combine", moe_combine_kernel<bf16, float>, dim3(n_tokens), dim3(block), 0, s,
-                             (const bf16*)y, place, weights, top, (const bf16*)shared, gate, width, (float*)out);
-    return st_launch_pdl("moe_combine", moe_combine_kernel<bf16, bf16>, dim3(n_tokens), dim3(block), 0, s, (const bf16*)y,
-                         place, weights, top, (const bf16*)shared, gate, width, (bf16*)out);
+    if (out_f32) {
+        if (vec) MC_LAUNCH(bf16, float, true);
+        MC_LAUNCH(bf16, float, false);
+    }
+    if (vec) MC_LAUNCH(bf16, bf16, true);
+    MC_LAUNCH(bf16, bf16, false);
+#undef MC_LAUNCH
 }
