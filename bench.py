@@ -155,8 +155,8 @@ def compare_designs(args, peaks):
         routed = {"type": "latent_attention", "mixer": mix,
                   "mlp": {"kind": "moe", "expert": {"ff": k["expert_ff"]}, "router": {"experts": k["experts"], "top": k["top"]},
                           "shared": {"ff": k["shared_ff"]}}}
-        pik = PikadraConfig.from_dict(dict(architecture="Pikadra", vocab=vocab, width=z["width"], norm={"eps": 1e-6},
-                                           embedding={"scale": 8.0}, logit_scale=0.25, logit_softcap=30.0,
+        pik = PikadraConfig.from_dict(dict(architecture="Pikadra", vocab=vocab, width=z["width"], norm={"eps": 1e-5},
+                                           embedding={"scale": 8.0}, logit_scale=0.5, logit_softcap=20.0,
                                            layers=[routed if i % 2 else dense for i in range(n_layers)]))
         all_designs = {"fanidra": fan, "pikadra": pik, "opt": opt}
         return {d: c for d, c in all_designs.items() if not args.designs or d in args.designs.split(",")}

@@ -120,14 +120,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
 
     for (int kt = kt_begin; kt < n_kt; ++kt) {
         const int stage = (kt - kt_begin) & 1;
-        if (kt + 1 < n_kt) {
-            load_keys(kt + 1, stage ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        cp_async_wait<0>();
+        __syncthreads();                 // this tile has landed, and every warp is through with the tile before
+        if (kt + 1 < n_kt) load_keys(kt + 1, stage ^ 1);      // into the stage the tile before was read from
+        cp_async_commit();
         const bf16* kb = sK + stage * LM_KEYS * lds;
         float s[NKT][4];
         {
@@ -231,7 +227,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
                 mma_bf16(o[2 * np + 1], a, b2, b3);
             }
         }
-        __syncthreads();
+        // no barrier here: the next turn's first one stands between these reads and the next writes
     }
     // the halves' sums meet; the sink joins the denominator; the gate multiplies
 #pragma unroll

@@ -392,7 +392,7 @@ CONFIGS = {
                                   layer(mixer(5, 6, 0, 9, 13, 7, 0.4), {"kind": "dense", "ff": 50})]),
                  seed=12, std=0.2, page_size=4),
     # the loop covers every layer and runs three times: the first pass opens before the first layer
-    "all": dict(cfg=dict(architecture="Pikadra", vocab=128, width=64, norm={"eps": 1e-6}, embedding={"scale": 8.0},
+    "all": dict(cfg=dict(architecture="Pikadra", vocab=128, width=64, norm={"eps": 2e-6}, embedding={"scale": 8.0},
                          logit_scale=1.0, logit_softcap=5.0, loop={"start": 0, "stop": 2, "times": 3},
                          layers=[layer(mixer(8, 16, 16, 16, 48, 24, 0.18, base=1000.0), moe(32, 9, 4, 32)),
                                  layer(mixer(2, 32, 8, 32, 64, 40, 0.15), {"kind": "dense", "ff": 96})]),
