@@ -50,7 +50,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
     for (int i = tid * 8; i < (LM_ROWS + 2 * LM_KEYS) * lds; i += LM_THREADS * 8)
         *reinterpret_cast<uint4*>(sQ + i) = make_uint4(0, 0, 0, 0);
     if (tid == 0) {
-        int tile = blockIdx.x, req = -1;
+        int tile = gridDim.x - 1 - blockIdx.x, req = -1;      // the last tiles of a request have the longest key ranges: first
         for (int i = 0; i < n_seqs; ++i) {
             const int rows = (q_start[i + 1] - q_start[i]) * nh;
             const int tiles = (rows + LM_ROWS - 1) / LM_ROWS;
@@ -298,7 +298,7 @@ latent_merge_kernel(const float* __restrict__ partial, int n_splits, int dvp, bf
     __shared__ float s_w[LM_MAX_SPLITS];
     __shared__ float s_k;
     if (threadIdx.x == 0) {
-        int tile = blockIdx.x, req = -1;
+        int tile = gridDim.x - 1 - blockIdx.x, req = -1;      // as in the attention kernel
         for (int i = 0; i < n_seqs; ++i) {
             const int rows = (q_start[i + 1] - q_start[i]) * nh;
             const int tiles = (rows + LM_ROWS - 1) / LM_ROWS;
