@@ -148,11 +148,11 @@ ST_EXPORT int st_gemm_grouped_plain(const void* a, const void* w, void* c, int n
 #define GM_LD (GM_BK + 8)
 #define GM_STAGES 3
 
-template <typename TO, bool GATED>
+template <typename TO, bool GATED, int BN>
 __global__ void __launch_bounds__(128)
 gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, TO* __restrict__ c, GroupedShape sh) {
     extern __shared__ __align__(16) unsigned char gm_smem[];
-    constexpr int WROWS = GATED ? 2 * GG_BN : GG_BN;
+    constexpr int WROWS = GATED ? 2 * BN : BN;
     bf16 (*sa)[GG_BM][GM_LD] = reinterpret_cast<bf16 (*)[GG_BM][GM_LD]>(gm_smem);
     bf16 (*sw)[WROWS][GM_LD] = reinterpret_cast<bf16 (*)[WROWS][GM_LD]>(gm_smem + sizeof(bf16) * GM_STAGES * GG_BM * GM_LD);
     __shared__ int srow[GG_BM];
@@ -177,7 +177,7 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
         srow[tid] = ar;
     }
     __syncthreads();
-    const int col0 = blockIdx.x * GG_BN;
+    const int col0 = blockIdx.x * BN;
     const bf16* wg = w + (long long)g * sh.w_gstride;
     const bf16* ag = a + g * sh.a_goff;
     auto load = [&](int k0, int stage) {
@@ -188,24 +188,25 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
             const bool ok = ar >= 0 && k0 + kc < sh.k_dim;
             cp_async16(&sa[stage][r][kc], ok ? ag + (long long)ar * sh.lda + k0 + kc : a, ok);
         }
-        for (int ch = tid; ch < GG_BN * 8 * (GATED ? 2 : 1); ch += 128) {
+        for (int ch = tid; ch < BN * 8 * (GATED ? 2 : 1); ch += 128) {
             const int r = ch >> 3, kc = (ch & 7) * 8;
-            const int n = col0 + (r & (GG_BN - 1)) + (r >= GG_BN ? sh.n_out : 0);
-            const bool ok = col0 + (r & (GG_BN - 1)) < sh.n_out && k0 + kc < sh.k_dim;
+            const int n = col0 + (r & (BN - 1)) + (r >= BN ? sh.n_out : 0);
+            const bool ok = col0 + (r & (BN - 1)) < sh.n_out && k0 + kc < sh.k_dim;
             cp_async16(&sw[stage][r][kc], ok ? wg + (long long)n * sh.k_dim + k0 + kc : w, ok);
         }
     };
-    float acc[2][4][4], acu[GATED ? 2 : 1][4][4];
+    constexpr int NJ = BN / 16;          // 8-wide output tiles of a warp (its half of the block's columns)
+    float acc[2][NJ][4], acu[GATED ? 2 : 1][NJ][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < NJ; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 acc[i][j][e] = 0.f;
                 if (GATED) acu[i][j][e] = 0.f;
             }
-    const int wm = (warp & 1) * 32, wn = (warp >> 1) * 32;
+    const int wm = (warp & 1) * 32, wn = (warp >> 1) * (BN / 2);
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
     const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
     const int n_k = (sh.k_dim + GM_BK - 1) / GM_BK;
@@ -229,7 +230,7 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
             for (int i = 0; i < 2; ++i)
                 ldmatrix_x4(af[i][0], af[i][1], af[i][2], af[i][3], &sa[stage][wm + i * 16 + a_row][kk + a_col]);
 #pragma unroll
-            for (int jp = 0; jp < 2; ++jp) {
+            for (int jp = 0; jp < NJ / 2; ++jp) {
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4(b0, b1, b2, b3, &sw[stage][wn + jp * 16 + b_row][kk + b_col]);
 #pragma unroll
@@ -238,7 +239,7 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
                     mma_bf16(acc[i][2 * jp + 1], af[i], b2, b3);
                 }
                 if (GATED) {
-                    ldmatrix_x4(b0, b1, b2, b3, &sw[stage][GG_BN + wn + jp * 16 + b_row][kk + b_col]);
+                    ldmatrix_x4(b0, b1, b2, b3, &sw[stage][BN + wn + jp * 16 + b_row][kk + b_col]);
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         mma_bf16(acu[i][2 * jp], af[i], b0, b1);
@@ -252,7 +253,7 @@ gemm_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, 
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < NJ; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int r = row0 + wm + i * 16 + gq + (e >> 1) * 8;
@@ -280,28 +281,32 @@ ST_EXPORT int st_gemm_grouped_mma(const void* a, const void* w, void* c, int n_g
                     a_rows, a_row_div};
     dim3 grid((n_out + GG_BN - 1) / GG_BN, offsets ? n_tiles : (n_rows + GG_BM - 1) / GG_BM, offsets ? 1 : n_groups);
     if (grid.y > 65535 || grid.z > 65535) return ST_ERR_TOO_LARGE;
+    // launches of few blocks (steps of few tokens, bound by the weights' way from memory) take tiles of 32 outputs:
+    // twice the blocks, so that every SM pulls weights
+    const bool narrow = (long long)grid.x * grid.y * grid.z < 2LL * st_sm_count();
+    if (narrow) grid.x = (n_out + 31) / 32;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_g = sizeof(bf16) * GM_STAGES * (GG_BM + 2 * GG_BN) * GM_LD, smem_p = sizeof(bf16) * GM_STAGES * (GG_BM + GG_BN) * GM_LD;
+    auto smem_of = [](int bn, bool g) { return sizeof(bf16) * GM_STAGES * (GG_BM + (g ? 2 : 1) * bn) * GM_LD; };
     static bool set = false;
     if (!set) {
-        cudaFuncSetAttribute(gemm_grouped_mma_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_g);
-        cudaFuncSetAttribute(gemm_grouped_mma_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_g);
-        cudaFuncSetAttribute(gemm_grouped_mma_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
-        cudaFuncSetAttribute(gemm_grouped_mma_kernel<bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);
+#define GM_SET(TO, G, BN) cudaFuncSetAttribute(gemm_grouped_mma_kernel<TO, G, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_of(BN, G))
+        GM_SET(float, true, 64); GM_SET(bf16, true, 64); GM_SET(float, false, 64); GM_SET(bf16, false, 64);
+        GM_SET(float, true, 32); GM_SET(bf16, true, 32); GM_SET(float, false, 32); GM_SET(bf16, false, 32);
+#undef GM_SET
         set = true;
     }
-    if (gated) {
-        if (out_f32)
-            return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<float, true>, grid, dim3(128), smem_g, s, (const bf16*)a,
-                                 (const bf16*)w, (float*)c, sh);
-        return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<bf16, true>, grid, dim3(128), smem_g, s, (const bf16*)a,
-                             (const bf16*)w, (bf16*)c, sh);
+#define GM_LAUNCH(TO, G, BN)                                                                                          \
+    return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<TO, G, BN>, grid, dim3(128), smem_of(BN, G), s,      \
+                         (const bf16*)a, (const bf16*)w, (TO*)c, sh)
+    if (narrow) {
+        if (gated) { if (out_f32) GM_LAUNCH(float, true, 32); GM_LAUNCH(bf16, true, 32); }
+        if (out_f32) GM_LAUNCH(float, false, 32);
+        GM_LAUNCH(bf16, false, 32);
     }
-    if (out_f32)
-        return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<float, false>, grid, dim3(128), smem_p, s, (const bf16*)a,
-                             (const bf16*)w, (float*)c, sh);
-    return st_launch_pdl("gemm_grouped", gemm_grouped_mma_kernel<bf16, false>, grid, dim3(128), smem_p, s, (const bf16*)a,
-                         (const bf16*)w, (bf16*)c, sh);
+    if (gated) { if (out_f32) GM_LAUNCH(float, true, 64); GM_LAUNCH(bf16, true, 64); }
+    if (out_f32) GM_LAUNCH(float, false, 64);
+    GM_LAUNCH(bf16, false, 64);
+#undef GM_LAUNCH
 }
 
 ST_EXPORT int st_gemm_grouped_tile_rows() { return GG_BM; }
