@@ -17,10 +17,19 @@
 // columns per warp / 8 (the block covers NT * 8 * NP >= kr columns; the template keeps the accumulator in registers).
 #include "latent_attention.cuh"
 #include "mma_sync.cuh"
+#include "tcgen05.cuh"
 
 #define LM_ROWS 64
 #define LM_KEYS 32
 #define LM_PLD 40          // row stride of the P tile in elements
+#define LM_LAZY 8.f        // how far (log2) a row's maximum may run ahead of the reference before the row is rescaled
+
+// one row of the cache into shared memory as a bulk copy that completes on an mbarrier (both addresses 16-byte
+// aligned, the size a multiple of 16 bytes)
+__device__ __forceinline__ void bulk_row_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(mbar) : "memory");
+}
 
 __device__ __forceinline__ void ldmatrix_x2_s(uint32_t& r0, uint32_t& r1, uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
@@ -41,6 +50,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
     float* smax = reinterpret_cast<float*>(sP + LM_ROWS * LM_PLD);  // [NP][64]
     float* ssum = smax + NP * LM_ROWS;                            // [NP][64]
     __shared__ int s_req, s_tile;
+    __shared__ __align__(8) uint64_t s_bar[2];          // "this stage's key rows have landed"
     constexpr int LM_THREADS = NP * 128, KW = LM_KEYS / NP, NKT = KW / 8;   // keys and key n-tiles of a warp
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, rg = warp & 3, half = warp >> 2;
     const int g = lane >> 2, tq = lane & 3;
@@ -59,7 +69,11 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
         }
         s_req = req;
         s_tile = tile;
+        tc_mbar_init(tc_smem(&s_bar[0]), 1);
+        tc_mbar_init(tc_smem(&s_bar[1]), 1);
+        tc_mbar_init_fence();
     }
+    tc_fence_async_smem();                              // the zeros above before the bulk copies into the same rows
     ST_PDL_WAIT();
     ST_PDL_TRIGGER();
     __syncthreads();
@@ -82,22 +96,25 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
             cp_async16(sQ + r * lds + ch * 8, src + (size_t)r * kd + ch * 8, r < rows_here);
         }
     }
-    // a warp owns some keys of a tile; its lanes walk the 16-byte chunks of the row
-    constexpr int KPW = LM_KEYS / (NP * 4);
+    // The key rows of a tile arrive as bulk copies, one per row, issued by the lanes of warp 0 (a lane per key: the 32
+    // page look-ups go out together) and completing on the stage's mbarrier; rows past the tile's last key keep what
+    // an earlier tile left there (finite numbers, and every weight on them is zero).
+    const uint32_t row_bytes = (uint32_t)kd * sizeof(bf16);
     auto load_keys = [&](int kt, int stage) {
-        bf16* dst = sK + (stage * LM_KEYS + warp * KPW) * lds;
-#pragma unroll
-        for (int kk = 0; kk < KPW; ++kk) {
-            const int j = kt * LM_KEYS + warp * KPW + kk;
-            bool ok = j < hi;
-            const bf16* src = pool;
-            if (ok) {
-                const int page = bt[j / ps];
-                if (page >= 0) src = latent_row(pool, cache, page, j % ps);
-                else { ok = false; if (status) *status = 1; }
-            }
-            for (int ch = lane; ch < chunks; ch += 32) cp_async16(dst + kk * lds + ch * 8, ok ? src + ch * 8 : pool, ok);
+        if (warp != 0) return;
+        const int j = kt * LM_KEYS + lane;
+        bool ok = j < hi;
+        const bf16* src = pool;
+        if (ok) {
+            const int page = bt[j / ps];
+            if (page >= 0) src = latent_row(pool, cache, page, j % ps);
+            else { ok = false; if (status) *status = 1; }
         }
+        const uint32_t bar = tc_smem(&s_bar[stage]);
+        const unsigned live = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) tc_mbar_expect_tx(bar, __popc(live) * row_bytes);
+        __syncwarp();
+        if (ok) bulk_row_copy(smem_u32(sK + (stage * LM_KEYS + lane) * lds), src, row_bytes, bar);
     };
     // the tile's key range, cut over blockIdx.y into parts of whole key tiles
     const int all_kt = (hi + LM_KEYS - 1) / LM_KEYS;
@@ -120,7 +137,8 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
 
     for (int kt = kt_begin; kt < n_kt; ++kt) {
         const int stage = (kt - kt_begin) & 1;
-        cp_async_wait<0>();
+        cp_async_wait<0>();              // the queries (first turn)
+        if (!tc_wait(tc_smem(&s_bar[stage]), ((kt - kt_begin) >> 1) & 1) && status) *status = 6;   // gave up: the step is invalid
         __syncthreads();                 // this tile has landed, and every warp is through with the tile before
         if (kt + 1 < n_kt) load_keys(kt + 1, stage ^ 1);      // into the stage the tile before was read from
         cp_async_commit();
@@ -188,8 +206,18 @@ latent_attention_mma_kernel(const bf16* __restrict__ q_lat, const bf16* __restri
             float mn = m[i];
 #pragma unroll
             for (int p = 0; p < NP; ++p) mn = fmaxf(mn, smax[p * LM_ROWS + row]);
-            corr[i] = m[i] == -INFINITY ? 0.f : fast_exp2(m[i] - mn);
-            m[i] = mn;
+            // m is the reference the row's weights are taken against, not its exact maximum: it moves only when the
+            // maximum has grown by more than LM_LAZY (in powers of two), so that the accumulator is rarely rescaled;
+            // weights stay below 2^LM_LAZY, and the reference cancels in the end like a maximum does
+            if (m[i] == -INFINITY) {
+                corr[i] = 1.f;                 // nothing accumulated yet
+                m[i] = mn;
+            } else if (mn > m[i] + LM_LAZY) {
+                corr[i] = fast_exp2(m[i] - mn);
+                m[i] = mn;
+            } else {
+                corr[i] = 1.f;
+            }
         }
         float add[2] = {0.f, 0.f};
 #pragma unroll

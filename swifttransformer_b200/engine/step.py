@@ -428,6 +428,9 @@ class ModelRunner:
             if code == 5:
                 raise RuntimeError("the tcgen05 matrix product gave up waiting for its copies or products; "
                                    "the step's result is invalid")
+            if code == 6:
+                raise RuntimeError("the latent attention kernel gave up waiting for its key rows; "
+                                   "the step's result is invalid")
             if code in (3, 4):
                 raise RuntimeError("the tcgen05 attention kernel gave up waiting for the tensor cores; "
                                    "the step's result is invalid")
